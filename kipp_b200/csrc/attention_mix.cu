@@ -27,7 +27,9 @@
 //                   mean square over the value size and multiplied by diff_scale;
 //   values_in_keys  the value of a key is the first v_dim elements of its key row (a latent that is
 //                   both key and value; there are no value pages);
-//   gate            head h of token t is multiplied by sigmoid(gate[t, gate_off + h]).
+//   gate            head h of token t is multiplied by sigmoid(gate[t, gate_off + h]);
+//   chunk           instead of a window: the positions are cut into blocks of `chunk` counted from
+//                   position 0 of the sequence, and a query sees the keys j <= p of its own block.
 //
 // attention_mix_kernel: one block per token (and, in steps of few tokens, per run of
 // SPLIT_TILES key tiles of that token: the runs' partial results -- maximum, sum and
@@ -80,9 +82,12 @@ __device__ __forceinline__ float dot_row(const float* __restrict__ qs, const bf1
 }
 
 // The visible keys of position p as two runs: [0, kept) and [first, p].
-__device__ __forceinline__ void visible_runs(int pos, int window, int keep_first, int& first, int& kept) {
-    first = window > 0 ? max(0, pos - window + 1) : 0;
-    kept = min(keep_first, first);
+__device__ __forceinline__ int first_visible(int pos, int window, int chunk) {
+    return chunk > 0 ? pos - pos % chunk : (window > 0 ? max(0, pos - window + 1) : 0);
+}
+__device__ __forceinline__ void visible_runs(int pos, int window, int keep_first, int chunk, int& first, int& kept) {
+    first = first_visible(pos, window, chunk);
+    kept = chunk > 0 ? 0 : min(keep_first, first);
 }
 
 constexpr int SPLIT_TILES = 2;     // key tiles per run when a step's tokens are cut into runs
@@ -97,6 +102,7 @@ struct MixExtras {
     const void* gate;          // [tokens, ld_gate] in the compute type, or null
     long long ld_gate;
     int gate_off;
+    int chunk;                 // > 0: blocks of this many positions bound what a query sees (no window then)
 };
 
 __device__ __forceinline__ float sigmoid_(float x) { return 1.0f / (1.0f + expf(-x)); }
@@ -210,7 +216,7 @@ attention_mix_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __re
     const int t = blockIdx.x;
     const int pos = positions[t];
     int first, kept;
-    visible_runs(pos, window, keep_first, first, kept);
+    visible_runs(pos, window, keep_first, ex.chunk, first, kept);
     const int kept_tiles = (kept + KT - 1) / KT;
     const int win0 = first / KT;
     const int n_tiles = kept_tiles + pos / KT - win0 + 1;
@@ -350,7 +356,7 @@ attention_mix_merge_kernel(T* __restrict__ out, const float* __restrict__ partia
     const int t = blockIdx.x, pos = positions[t], h_first = blockIdx.y * MERGE_HEADS;
     const int nh = min(MERGE_HEADS, n_q - h_first);
     int first, kept;
-    visible_runs(pos, window, keep_first, first, kept);
+    visible_runs(pos, window, keep_first, ex.chunk, first, kept);
     const int n_tiles = (kept + KT - 1) / KT + pos / KT - first / KT + 1;
     const int runs = min(max_runs, (n_tiles + SPLIT_TILES - 1) / SPLIT_TILES);
     const float* src = partial + (size_t)t * max_runs * n_q * (v_dim + 2);
@@ -541,8 +547,8 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
 
     // key tiles any query of the block sees: the kept tokens that lie before the window's first
     // tile, then the window's tiles (a kept token inside those is met there)
-    const int first_lo = window > 0 ? max(0, pos0 - window + 1) : 0;
-    const int kept_hi = window > 0 ? min(keep_first, pos_hi + 1) : 0;
+    const int first_lo = first_visible(pos0, window, ex.chunk);
+    const int kept_hi = window > 0 && ex.chunk == 0 ? min(keep_first, pos_hi + 1) : 0;
     const int win0 = first_lo / KT;
     const int kept_only = min((kept_hi + KT - 1) / KT, win0);
     const int n_tiles = kept_only + pos_hi / KT - win0 + 1;
@@ -620,7 +626,8 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
         constexpr int RI = 4;
         static_assert(MMA_THREADS / 32 == QB, "one warp per query of the block");
         const int r = warp, pos = pos0 + r, j = j0 + lane;
-        const bool vis = r < n_tok && pg[lane] >= 0 && j <= pos && (window == 0 || pos - j < window || j < keep_first);
+        const bool vis = r < n_tok && pg[lane] >= 0 && j <= pos &&
+                         (ex.chunk > 0 ? j >= pos - pos % ex.chunk : (window == 0 || pos - j < window || j < keep_first));
         for (int h0 = 0; h0 < n_q; h0 += RI) {
             float sv[RI], m_old[RI], mx[RI], p[RI], c[RI], ps[RI];
             int rows[RI];
@@ -876,7 +883,7 @@ attention_shared_key_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, 
     const int gid = lane >> 2, tig = lane & 3;
     const int t = blockIdx.x, h0 = blockIdx.y * SK_ROWS;
     const int pos = positions[t];
-    const int first = window > 0 ? max(0, pos - window + 1) : 0;
+    const int first = first_visible(pos, window, ex.chunk);
     const int win0 = first / KT;
     const int n_tiles = pos / KT - win0 + 1;
     const int it0 = split ? blockIdx.z * SPLIT_TILES : 0;
@@ -1198,7 +1205,7 @@ extern "C" int kipp_attention_mix_ex(void* out, const void* q, const void* k_pag
     ex.key_maps = 1;
     if (extras != nullptr) ex = *static_cast<const MixExtras*>(extras);
     if (ex.key_maps < 1 || (n_q / n_kv) % ex.key_maps || (ex.diff && ex.key_maps != 2) ||
-        (ex.values_in_keys && v_dim > ex.key_maps * head_dim))
+        (ex.values_in_keys && v_dim > ex.key_maps * head_dim) || ex.chunk < 0 || (ex.chunk > 0 && window > 0))
         return KIPP_ERR_ARG;
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == KIPP_DT_F32)

@@ -299,3 +299,115 @@ extern "C" int kipp_activation(void* out, long long ld_out, const void* z, long 
                            (const bf16*)z, ld_z, rows, n, kind);
     return KIPP_ERR_DTYPE;
 }
+
+// ---------------------------------------------------------------------------
+// A second embedding table addressed by a hash of the token pair: x[t, :] += table[row(t), :] with
+// row = (previous token * mul_prev + token * mul_cur) mod buckets, and row = buckets (the table's
+// extra last row) for the token at position 0 of its sequence.  The previous token of a step's
+// first token is the one the sequence's slot keeps (last_token[slot * stride], written by
+// kipp_keep_last_token after this kernel: the token before is part of a sequence's state).
+template <typename TW>
+__global__ void hashed_pair_add_kernel(float* __restrict__ x, const TW* __restrict__ table,
+                                       const int* __restrict__ ids, const int* __restrict__ positions,
+                                       const int* __restrict__ entry_of_token, const int* __restrict__ q_start,
+                                       const int* __restrict__ slots, const int* __restrict__ last_token,
+                                       long long stride, int hidden, int vocab, long long buckets, long long mul_prev,
+                                       long long mul_cur, int* __restrict__ status) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const int id = ids[t], e = entry_of_token[t];
+    long long row = buckets;
+    if (positions[t] > 0) {
+        const int prev = t > q_start[e] ? ids[t - 1] : last_token[(size_t)slots[e] * stride];
+        if (id < 0 || id >= vocab || prev < 0 || prev >= vocab) {      // never read outside the table
+            if (threadIdx.x == 0) atomicExch(status, 1);
+            return;
+        }
+        row = ((long long)prev * mul_prev + (long long)id * mul_cur) % buckets;
+    }
+    const TW* src = table + (size_t)row * hidden;
+    float* dst = x + (size_t)t * hidden;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] += to_f32(src[i]);
+}
+
+extern "C" int kipp_hashed_pair_add(float* x, const void* table, int table_dtype, const int* ids, const int* positions,
+                                    const int* entry_of_token, const int* q_start, const int* slots,
+                                    const int* last_token, long long stride, int tokens, int hidden, int vocab,
+                                    long long buckets, long long mul_prev, long long mul_cur, int* status, void* stream) {
+    if (tokens <= 0) return 0;
+    if (hidden <= 0 || vocab <= 0 || buckets <= 0 || mul_prev < 0 || mul_cur < 0 || last_token == nullptr || stride <= 0)
+        return KIPP_ERR_ARG;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = hidden >= 1024 ? 256 : 128;
+    if (table_dtype == KIPP_DT_F32)
+        return kipp_launch(hashed_pair_add_kernel<float>, dim3(tokens), dim3(threads), 0, s, 1, x, (const float*)table, ids,
+                           positions, entry_of_token, q_start, slots, last_token, stride, hidden, vocab, buckets, mul_prev,
+                           mul_cur, status);
+    if (table_dtype == KIPP_DT_BF16)
+        return kipp_launch(hashed_pair_add_kernel<bf16>, dim3(tokens), dim3(threads), 0, s, 1, x, (const bf16*)table, ids,
+                           positions, entry_of_token, q_start, slots, last_token, stride, hidden, vocab, buckets, mul_prev,
+                           mul_cur, status);
+    return KIPP_ERR_DTYPE;
+}
+
+// last_token[slots[e] * stride] = the last token entry e brings in this step.
+__global__ void keep_last_token_kernel(int* __restrict__ last_token, long long stride, const int* __restrict__ ids,
+                                       const int* __restrict__ q_start, const int* __restrict__ slots, int entries) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e < entries && q_start[e + 1] > q_start[e]) last_token[(size_t)slots[e] * stride] = ids[q_start[e + 1] - 1];
+}
+
+extern "C" int kipp_keep_last_token(int* last_token, long long stride, const int* ids, const int* q_start,
+                                    const int* slots, int entries, void* stream) {
+    if (entries <= 0) return 0;
+    if (last_token == nullptr || stride <= 0) return KIPP_ERR_ARG;
+    return kipp_launch(keep_last_token_kernel, dim3((unsigned)((entries + 127) / 128)), dim3(128), 0, (cudaStream_t)stream, 1,
+                       last_token, stride, ids, q_start, slots, entries);
+}
+
+// ---------------------------------------------------------------------------
+// x[r, :] += mult * y[r, :] * rsqrt(mean(y[r, :]^2) + eps) * w: the RMS norm of a sublayer's OUTPUT
+// joins the residual stream, all of it float32 (w keeps its storage type).
+__global__ void __launch_bounds__(256)
+rmsnorm_scaled_add_kernel(float* __restrict__ x, const float* __restrict__ y, const void* __restrict__ w, int w_dtype,
+                          int size, float eps, float mult) {
+    __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
+    const float* src = y + (size_t)blockIdx.x * size;
+    float* dst = x + (size_t)blockIdx.x * size;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < size; i += blockDim.x) ss = fmaf(src[i], src[i], ss);
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)size + eps);
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        const float wi = w_dtype == KIPP_DT_F32 ? static_cast<const float*>(w)[i] : to_f32(static_cast<const bf16*>(w)[i]);
+        dst[i] += mult * (src[i] * inv * wi);
+    }
+}
+
+extern "C" int kipp_rmsnorm_scaled_add(float* x, const float* y, const void* w, int w_dtype, int rows, int size, float eps,
+                                       float mult, void* stream) {
+    if (rows <= 0) return 0;
+    if (size <= 0 || !(eps > 0.f) || (w_dtype != KIPP_DT_F32 && w_dtype != KIPP_DT_BF16)) return KIPP_ERR_ARG;
+    return kipp_launch(rmsnorm_scaled_add_kernel, dim3((unsigned)rows), dim3(size >= 1024 ? 256 : 128), 0, (cudaStream_t)stream,
+                       1, x, y, w, w_dtype, size, eps, mult);
+}
+
+// x *= scale over n float32 values (logits of a head with a scale).
+__global__ void scale_f32_kernel(float* __restrict__ x, long long n, float scale) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] *= scale;
+}
+
+extern "C" int kipp_scale_f32(float* x, long long n, float scale, void* stream) {
+    if (n <= 0) return 0;
+    const long long blocks = (n + 255) / 256;
+    if (blocks > 0x7fffffffLL) return KIPP_ERR_ARG;
+    return kipp_launch(scale_f32_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, 1, x, n, scale);
+}

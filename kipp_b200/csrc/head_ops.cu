@@ -5,9 +5,10 @@
 // segment says where its heads lie, what is done to them and where they go:
 //   bias       a float32 vector added first (the projection's bias);
 //   norm       division of the head by its root mean square (eps inside the root), times a
-//              weight of the head's size;
+//              weight of the head's size; or (norm_all) division of ALL heads of the segment by the
+//              root mean square of the whole run of heads x dim columns, times a weight of that size;
 //   rotation   of the dims [rot_off, rot_off + rot) of the head: pair (i, i + rot/2) turns by the
-//              angle of the step's (cos, sin) table for the token;
+//              angle of the step's (cos, sin) table for the token; or (interleaved) pair (2i, 2i + 1);
 //   target     a row of an activation buffer (queries), or the token's slot in the key or value
 //              pages, where several heads of a segment may share one page row side by side
 //              (two score maps of one key head; a latent and a rotated part that form one key).
@@ -31,8 +32,10 @@ struct HeadSegment {
     int target;                              // 0 activation rows, 1 key pages, 2 value pages
     int dst_off, dst_stride;                 // activation: head i at dst_off + i * dst_stride of the token's row
     int heads_per_row;                       // pages: this many heads side by side in one page row
+    int norm_all;                            // 1: one mean square over all heads of the segment, norm_w [heads * dim]
+    int interleaved;                         // 1: the rotation pairs dim 2i with dim 2i + 1
     const float* bias;                       // [heads * dim] or null
-    const float* norm_w;                     // [dim] or null
+    const float* norm_w;                     // [dim] ([heads * dim] with norm_all) or null
     const float* cos_sin;                    // [tokens, rot / 2, 2] or null
     void* dst;                               // activation buffer of the compute type (target 0)
     long long ld_dst;
@@ -86,7 +89,19 @@ head_segments_kernel(const SegmentArgs a, int* __restrict__ status) {
     }
 
     float inv = 1.f;
-    if (g.norm_w != nullptr) {
+    const float* norm_w = g.norm_w;
+    if (g.norm_w != nullptr && g.norm_all) {
+        // every warp of the token sums the whole run of heads in the same order
+        const T* all = static_cast<const T*>(a.src) + (size_t)t * a.ld_src + g.src_off;
+        const int n = g.heads * D;
+        float ss = 0.f;
+        for (int i = lane; i < n; i += 32) {
+            const float v = to_f32(all[i]) + (g.bias ? g.bias[i] : 0.f);
+            ss = fmaf(v, v, ss);
+        }
+        inv = 1.0f / sqrtf(warp_sum(ss) / (float)n + a.eps);
+        norm_w = g.norm_w + (size_t)hh * D;
+    } else if (g.norm_w != nullptr) {
         float ss = 0.f;
         for (int i = lane; i < D; i += 32) {
             const float v = to_f32(src[i]) + (bias ? bias[i] : 0.f);
@@ -99,17 +114,17 @@ head_segments_kernel(const SegmentArgs a, int* __restrict__ status) {
                                                            : nullptr;
     auto value = [&](int i) {
         float v = to_f32(src[i]) + (bias ? bias[i] : 0.f);
-        if (g.norm_w != nullptr) v = v * inv * g.norm_w[i];
+        if (norm_w != nullptr) v = v * inv * norm_w[i];
         return v;
     };
     for (int i = lane; i < D; i += 32) {
         float v = value(i);
         const int r = i - g.rot_off;
         if (cs != nullptr && r >= 0 && r < g.rot) {
-            // low half: u cos - v sin; high half: v cos + u sin (u the low half, v the high one)
-            const bool low = r < half;
-            const float2 c = cs[low ? r : r - half];
-            const float other = value(low ? i + half : i - half);
+            // first of a pair: u cos - v sin; second: v cos + u sin (u the first, v the second)
+            const bool low = g.interleaved ? (r & 1) == 0 : r < half;
+            const float2 c = cs[g.interleaved ? r >> 1 : (low ? r : r - half)];
+            const float other = value(g.interleaved ? (low ? i + 1 : i - 1) : (low ? i + half : i - half));
             v = low ? v * c.x - other * c.y : v * c.x + other * c.y;
         }
         if (into_cache) {
@@ -326,7 +341,7 @@ extern "C" int kipp_head_segments(const void* src, long long ld_src, int dtype, 
         const HeadSegment& g = seg[i];
         if (g.heads <= 0 || g.dim <= 0 || g.rot < 0 || (g.rot & 1) || g.rot_off < 0 || g.rot_off + g.rot > g.dim ||
             g.target < 0 || g.target > 2 || (g.target == 0 && g.dst == nullptr) || (g.target != 0 && g.heads_per_row <= 0) ||
-            (g.rot > 0 && g.cos_sin == nullptr))
+            (g.rot > 0 && g.cos_sin == nullptr) || (g.norm_all && g.src_stride != g.dim))
             return KIPP_ERR_ARG;
         if (g.target == 1 && (k_pages == nullptr || g.dst_off + g.heads_per_row * g.dim > k_row)) return KIPP_ERR_ARG;
         if (g.target == 2 && (v_pages == nullptr || g.dst_off + g.heads_per_row * g.dim > v_row)) return KIPP_ERR_ARG;

@@ -88,7 +88,8 @@ struct AttentionExtras {
     const void* gate = nullptr;
     long long ld_gate = 0;
     int gate_off = 0;
-    bool any() const { return sink || key_maps != 1 || values_in_keys || diff || gate; }
+    int chunk = 0;                         // > 0: a query sees the keys j <= p of its own block of `chunk` positions
+    bool any() const { return sink || key_maps != 1 || values_in_keys || diff || gate || chunk; }
 };
 
 // A run of heads in a projection row and what becomes of them (the layout is the kernel
@@ -99,6 +100,8 @@ struct HeadSegment {
     int target = 0;                        // 0 activation rows, 1 key pages, 2 value pages
     int dst_off = 0, dst_stride = 0;
     int heads_per_row = 1;
+    int norm_all = 0;                      // 1: one mean square over all heads of the segment, norm_w [heads * dim]
+    int interleaved = 0;                   // 1: the rotation pairs dim 2i with dim 2i + 1
     const float* bias = nullptr;
     const float* norm_w = nullptr;
     const float* cos_sin = nullptr;
@@ -315,7 +318,10 @@ public:
             return;
         }
         // a step of few tokens is cut into runs of keys (the table's width bounds the context)
-        const int runs = runs_of(tokens, window, keep_first, cache.table_width * cache.page_size);
+        // (a block of positions spans as many key tiles as a window of its size)
+        const int chunk = extras != nullptr ? extras->chunk : 0;
+        const int runs = runs_of(tokens, chunk > 0 ? chunk : window, chunk > 0 ? 0 : keep_first,
+                                 cache.table_width * cache.page_size);
         float* partial = runs > 1 ? workspace->get<float>("attention_mix_runs", (size_t)scratch_of(tokens, runs, n_q, v_dim))
                                   : nullptr;
         // one key row per token that is also its value (a latent), all heads on it: the heads of a

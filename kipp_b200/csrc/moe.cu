@@ -1,0 +1,362 @@
+// A feed-forward made of many small experts of which every token uses a few.
+//
+//   route     z = W_r h + b in float32 (a warp per token); the `top` largest logits are chosen (the
+//             lower index on a tie) and their weights are the softmax over the chosen logits only;
+//   lists     the (token, choice) pairs sorted by expert, cut into tiles of 64 rows that belong to
+//             one expert each; everything on the device, so that a step's launches do not depend
+//             on the routing (a captured graph replays them);
+//   products  per tile: rows gathered from the tokens' input times the expert's up projection,
+//             with the activation, into a hidden buffer in sorted order; then the hidden rows
+//             times the expert's down projection into one float32 row per pair;
+//   combine   y[t] += sum over the token's choices, in the order of their rank, of weight x row.
+//
+// A pair's row is computed from its own token alone, in an order of sums that depends on the
+// sizes only: the result does not depend on which other tokens share its tile.  The products run
+// on the tensor cores (mma.sync m16n8k16, bfloat16 in, float32 sums) or, in 32-bit and for sizes
+// that are no multiple of 8, on the CUDA cores.
+#include "common.cuh"
+#include <math.h>
+#include <limits.h>
+
+namespace {
+constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_route_kernel(int* __restrict__ expert_of, float* __restrict__ weight_of, const T* __restrict__ h, long long ldh,
+                 const float* __restrict__ router, const float* __restrict__ bias, int tokens, int hidden, int experts,
+                 int top) {
+    extern __shared__ float z_all[];                      // [warps][experts]
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
+    if (t >= tokens) return;
+    float* z = z_all + (size_t)warp * experts;
+    const T* row = h + (size_t)t * ldh;
+    for (int e = 0; e < experts; ++e) {
+        const float* w = router + (size_t)e * hidden;
+        float acc = 0.f;
+        for (int i = lane; i < hidden; i += 32) acc = fmaf(w[i], to_f32(row[i]), acc);
+        acc = warp_sum(acc);
+        if (lane == 0) z[e] = acc + (bias ? bias[e] : 0.f);
+    }
+    __syncwarp();
+    for (int k = 0; k < top; ++k) {
+        float best = -INFINITY;
+        int idx = INT_MAX;
+        for (int e = lane; e < experts; e += 32) {
+            const float v = z[e];
+            if (v > best) { best = v; idx = e; }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+            if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+        }
+        if (idx >= experts) { idx = k; best = 0.f; }      // logits that are no numbers: still a valid expert
+        if (lane == 0) {
+            expert_of[(size_t)t * top + k] = idx;
+            weight_of[(size_t)t * top + k] = best;
+            z[idx] = -INFINITY;
+        }
+        __syncwarp();
+    }
+    if (lane == 0) {
+        float* w = weight_of + (size_t)t * top;
+        const float m = w[0];                            // the largest of the chosen
+        float sum = 0.f;
+        for (int k = 0; k < top; ++k) { w[k] = expf(w[k] - m); sum += w[k]; }
+        const float inv = 1.0f / sum;
+        for (int k = 0; k < top; ++k) w[k] *= inv;
+    }
+}
+
+// tile_info: (expert, first row in the sorted list, rows) per tile
+__global__ void __launch_bounds__(1024)
+moe_lists_kernel(int* __restrict__ sorted_pair, int* __restrict__ tile_info, int* __restrict__ n_tiles,
+                 const int* __restrict__ expert_of, int pairs, int experts) {
+    extern __shared__ int lists[];                        // counts [experts], cursor [experts]
+    int* counts = lists;
+    int* cursor = lists + experts;
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&counts[expert_of[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int off = 0, nt = 0;
+        for (int e = 0; e < experts; ++e) {
+            cursor[e] = off;
+            for (int r0 = 0; r0 < counts[e]; r0 += BM) {
+                tile_info[3 * nt] = e;
+                tile_info[3 * nt + 1] = off + r0;
+                tile_info[3 * nt + 2] = min(BM, counts[e] - r0);
+                ++nt;
+            }
+            off += counts[e];
+        }
+        *n_tiles = nt;
+    }
+    __syncthreads();
+    // a pair's place among its expert's rows is whatever the race gives: its row's value does not depend on it
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) sorted_pair[atomicAdd(&cursor[expert_of[p]], 1)] = p;
+}
+
+struct GemmArgs {
+    void* out; long long ldo;
+    const void* a; long long lda;
+    const void* w; long long w_expert;      // elements between two experts' matrices [N, K]
+    int N, K, top, gather, scatter, act;
+    const int* sorted_pair; const int* tile_info; const int* n_tiles;
+};
+
+// CUDA cores: a block of 256 threads per 64 x 64 tile, each thread 4 x 4 results.
+template <typename T, typename TO>
+__global__ void __launch_bounds__(256)
+moe_gemm_kernel(const GemmArgs g) {
+    __shared__ float As[BK][BM + 4];
+    __shared__ float Ws[BK][BN + 4];
+    __shared__ int arow[BM], orow[BM];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tile = blockIdx.y;
+    if (tile >= *g.n_tiles) return;
+    const int e = g.tile_info[3 * tile], r0 = g.tile_info[3 * tile + 1], rows = g.tile_info[3 * tile + 2];
+    const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
+    if (tid < BM) {
+        const int pair = tid < rows ? g.sorted_pair[r0 + tid] : -1;
+        arow[tid] = pair < 0 ? -1 : (g.gather ? pair / g.top : r0 + tid);
+        orow[tid] = pair < 0 ? -1 : (g.scatter ? pair : r0 + tid);
+    }
+    __syncthreads();
+    const T* A = static_cast<const T*>(g.a);
+    const T* W = static_cast<const T*>(g.w) + (size_t)e * g.w_expert;
+    const int n0 = blockIdx.x * BN, N = g.N, K = g.K;
+    float acc[TM][TN];
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+    const int lrow = tid >> 2, lk = (tid & 3) * 4;
+    const int ar = arow[lrow];
+    for (int k0 = 0; k0 < K; k0 += BK) {
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+            const int k = k0 + lk + i, wn = n0 + lrow;
+            As[lk + i][lrow] = (ar >= 0 && k < K) ? to_f32(A[(size_t)ar * g.lda + k]) : 0.f;
+            Ws[lk + i][lrow] = (wn < N && k < K) ? to_f32(W[(size_t)wn * K + k]) : 0.f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int k = 0; k < BK; ++k) {
+            float x[TM], y[TN];
+#pragma unroll
+            for (int i = 0; i < TM; ++i) x[i] = As[k][ty * TM + i];
+#pragma unroll
+            for (int j = 0; j < TN; ++j) y[j] = Ws[k][tx * TN + j];
+#pragma unroll
+            for (int i = 0; i < TM; ++i)
+#pragma unroll
+                for (int j = 0; j < TN; ++j) acc[i][j] = fmaf(x[i], y[j], acc[i][j]);
+        }
+        __syncthreads();
+    }
+    TO* out = static_cast<TO*>(g.out);
+#pragma unroll
+    for (int i = 0; i < TM; ++i) {
+        const int orw = orow[ty * TM + i];
+        if (orw < 0) continue;
+#pragma unroll
+        for (int j = 0; j < TN; ++j) {
+            const int n = n0 + tx * TN + j;
+            if (n < N) out[(size_t)orw * g.ldo + n] = from_f32<TO>(g.act >= 0 ? kipp_activation(acc[i][j], g.act) : acc[i][j]);
+        }
+    }
+}
+
+__device__ __forceinline__ void mma_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ void cp16(void* dst, const void* src, bool ok) {
+    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
+    const int n = ok ? 16 : 0;
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n));
+}
+
+// Tensor cores: a block of 4 warps per 64 rows x 128 features; K in steps of 32 through two shared
+// buffers filled by asynchronous copies.  Warp w owns features [32 w, 32 w + 32) of all 64 rows.
+constexpr int TBN = 128, TBK = 32, TLD = TBK + 8;
+template <typename TO>
+__global__ void __launch_bounds__(128)
+moe_gemm_mma_kernel(const GemmArgs g) {
+    __shared__ __align__(16) bf16 As[2][BM][TLD];
+    __shared__ __align__(16) bf16 Ws[2][TBN][TLD];
+    __shared__ int arow[BM], orow[BM];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int tile = blockIdx.y;
+    if (tile >= *g.n_tiles) return;
+    const int e = g.tile_info[3 * tile], r0 = g.tile_info[3 * tile + 1], rows = g.tile_info[3 * tile + 2];
+    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
+    if (tid < BM) {
+        const int pair = tid < rows ? g.sorted_pair[r0 + tid] : -1;
+        arow[tid] = pair < 0 ? -1 : (g.gather ? pair / g.top : r0 + tid);
+        orow[tid] = pair < 0 ? -1 : (g.scatter ? pair : r0 + tid);
+    }
+    __syncthreads();
+    const bf16* A = static_cast<const bf16*>(g.a);
+    const bf16* W = static_cast<const bf16*>(g.w) + (size_t)e * g.w_expert;
+    const int n0 = blockIdx.x * TBN, N = g.N, K = g.K;
+    auto load = [&](int buf, int k0) {
+        // 64 rows x 4 chunks of A, 128 rows x 4 chunks of W: 16-byte chunks of 8 elements
+        for (int i = tid; i < BM * 4; i += 128) {
+            const int r = i >> 2, c = (i & 3) * 8;
+            const bool ok = arow[r] >= 0 && k0 + c < K;
+            cp16(&As[buf][r][c], ok ? A + (size_t)arow[r] * g.lda + k0 + c : A, ok);
+        }
+        for (int i = tid; i < TBN * 4; i += 128) {
+            const int r = i >> 2, c = (i & 3) * 8;
+            const bool ok = n0 + r < N && k0 + c < K;
+            cp16(&Ws[buf][r][c], ok ? W + (size_t)(n0 + r) * K + k0 + c : W, ok);
+        }
+        asm volatile("cp.async.commit_group;");
+    };
+    float acc[4][4][4];
+#pragma unroll
+    for (int m = 0; m < 4; ++m)
+#pragma unroll
+        for (int n = 0; n < 4; ++n) acc[m][n][0] = acc[m][n][1] = acc[m][n][2] = acc[m][n][3] = 0.f;
+    load(0, 0);
+    int buf = 0;
+    for (int k0 = 0; k0 < K; k0 += TBK, buf ^= 1) {
+        if (k0 + TBK < K) load(buf ^ 1, k0 + TBK);
+        else asm volatile("cp.async.commit_group;");
+        asm volatile("cp.async.wait_group 1;");
+        __syncthreads();
+#pragma unroll
+        for (int ks = 0; ks < TBK; ks += 16) {
+            uint32_t b[4][2];
+#pragma unroll
+            for (int n = 0; n < 4; ++n) {
+                const bf16* wr = &Ws[buf][warp * 32 + n * 8 + gid][ks + tig * 2];
+                b[n][0] = *reinterpret_cast<const uint32_t*>(wr);
+                b[n][1] = *reinterpret_cast<const uint32_t*>(wr + 8);
+            }
+#pragma unroll
+            for (int m = 0; m < 4; ++m) {
+                uint32_t a[4];
+                const bf16* ar = &As[buf][m * 16 + gid][ks + tig * 2];
+                a[0] = *reinterpret_cast<const uint32_t*>(ar);
+                a[1] = *reinterpret_cast<const uint32_t*>(ar + 8 * TLD);
+                a[2] = *reinterpret_cast<const uint32_t*>(ar + 8);
+                a[3] = *reinterpret_cast<const uint32_t*>(ar + 8 * TLD + 8);
+#pragma unroll
+                for (int n = 0; n < 4; ++n) mma_16816(acc[m][n], a, b[n][0], b[n][1]);
+            }
+        }
+        __syncthreads();
+    }
+    TO* out = static_cast<TO*>(g.out);
+#pragma unroll
+    for (int m = 0; m < 4; ++m)
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int orw = orow[m * 16 + gid + half * 8];
+            if (orw < 0) continue;
+#pragma unroll
+            for (int n = 0; n < 4; ++n)
+#pragma unroll
+                for (int j = 0; j < 2; ++j) {
+                    const int col = n0 + warp * 32 + n * 8 + tig * 2 + j;
+                    const float v = acc[m][n][half * 2 + j];
+                    if (col < N) out[(size_t)orw * g.ldo + col] = from_f32<TO>(g.act >= 0 ? kipp_activation(v, g.act) : v);
+                }
+        }
+}
+
+__global__ void __launch_bounds__(128)
+moe_combine_kernel(float* __restrict__ y, const float* __restrict__ rows, const float* __restrict__ weight_of, int hidden,
+                   int top) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const float* w = weight_of + (size_t)t * top;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k) acc = fmaf(w[k], rows[((size_t)t * top + k) * hidden + i], acc);
+        y[(size_t)t * hidden + i] += acc;
+    }
+}
+}  // namespace
+
+// Tiles a step of `pairs` (token, choice) pairs over `experts` experts can need at most.
+extern "C" int kipp_moe_max_tiles(int pairs, int experts) { return (pairs + BM - 1) / BM + experts; }
+
+// expert_of, weight_of [tokens, top]: the chosen experts in the order of their logits and their weights.
+extern "C" int kipp_moe_route(int* expert_of, float* weight_of, const void* h, long long ldh, int dtype, const float* router,
+                              const float* bias, int tokens, int hidden, int experts, int top, void* stream) {
+    if (tokens <= 0) return 0;
+    if (hidden <= 0 || experts <= 0 || top <= 0 || top > experts || experts > 2048) return KIPP_ERR_ARG;
+    const dim3 grid((unsigned)((tokens + 3) / 4));
+    const size_t smem = (size_t)4 * experts * sizeof(float);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == KIPP_DT_F32)
+        return kipp_launch(moe_route_kernel<float>, grid, dim3(128), smem, s, 1, expert_of, weight_of, (const float*)h, ldh,
+                           router, bias, tokens, hidden, experts, top);
+    if (dtype == KIPP_DT_BF16)
+        return kipp_launch(moe_route_kernel<bf16>, grid, dim3(128), smem, s, 1, expert_of, weight_of, (const bf16*)h, ldh,
+                           router, bias, tokens, hidden, experts, top);
+    return KIPP_ERR_DTYPE;
+}
+
+// sorted_pair [pairs], tile_info [3 x kipp_moe_max_tiles], n_tiles [1]
+extern "C" int kipp_moe_lists(int* sorted_pair, int* tile_info, int* n_tiles, const int* expert_of, int pairs, int experts,
+                              void* stream) {
+    if (pairs <= 0) return 0;
+    if (experts <= 0 || experts > 2048) return KIPP_ERR_ARG;
+    return kipp_launch(moe_lists_kernel, dim3(1), dim3(1024), (size_t)2 * experts * sizeof(int), (cudaStream_t)stream, 1,
+                       sorted_pair, tile_info, n_tiles, expert_of, pairs, experts);
+}
+
+// One product of every tile: out rows = act(A rows x W[expert]^T).  gather: a row of A is the pair's
+// token (else its place in the sorted list); scatter: a row of out is the pair (else its place in the
+// sorted list).  A and W in `dtype`; out in `out_dtype`.  tensor_core 0 keeps the CUDA-core kernel.
+extern "C" int kipp_moe_gemm(void* out, int out_dtype, long long ldo, const void* a, long long lda, const void* w,
+                             long long w_expert, int dtype, int N, int K, int top, int gather, int scatter, int act,
+                             const int* sorted_pair, const int* tile_info, const int* n_tiles, int pairs, int experts,
+                             int tensor_core, void* stream) {
+    if (pairs <= 0) return 0;
+    if (N <= 0 || K <= 0 || top <= 0 || experts <= 0) return KIPP_ERR_ARG;
+    GemmArgs g;
+    g.out = out; g.ldo = ldo; g.a = a; g.lda = lda; g.w = w; g.w_expert = w_expert;
+    g.N = N; g.K = K; g.top = top; g.gather = gather; g.scatter = scatter; g.act = act;
+    g.sorted_pair = sorted_pair; g.tile_info = tile_info; g.n_tiles = n_tiles;
+    const int tiles = kipp_moe_max_tiles(pairs, experts);
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool aligned = K % 8 == 0 && lda % 8 == 0 && w_expert % 8 == 0 && (((uintptr_t)a | (uintptr_t)w) & 15) == 0;
+    if (dtype == KIPP_DT_BF16 && tensor_core && aligned) {
+        const dim3 grid((unsigned)((N + TBN - 1) / TBN), (unsigned)tiles);
+        if (out_dtype == KIPP_DT_BF16) return kipp_launch(moe_gemm_mma_kernel<bf16>, grid, dim3(128), 0, s, 1, g);
+        if (out_dtype == KIPP_DT_F32) return kipp_launch(moe_gemm_mma_kernel<float>, grid, dim3(128), 0, s, 1, g);
+        return KIPP_ERR_DTYPE;
+    }
+    const dim3 grid((unsigned)((N + BN - 1) / BN), (unsigned)tiles);
+    if (dtype == KIPP_DT_F32 && out_dtype == KIPP_DT_F32) return kipp_launch(moe_gemm_kernel<float, float>, grid, dim3(256), 0, s, 1, g);
+    if (dtype == KIPP_DT_BF16 && out_dtype == KIPP_DT_BF16) return kipp_launch(moe_gemm_kernel<bf16, bf16>, grid, dim3(256), 0, s, 1, g);
+    if (dtype == KIPP_DT_BF16 && out_dtype == KIPP_DT_F32) return kipp_launch(moe_gemm_kernel<bf16, float>, grid, dim3(256), 0, s, 1, g);
+    return KIPP_ERR_DTYPE;
+}
+
+// y[t, :] += sum_k weight_of[t, k] * rows[t * top + k, :], k in order.
+extern "C" int kipp_moe_combine(float* y, const float* rows, const float* weight_of, int tokens, int hidden, int top,
+                                void* stream) {
+    if (tokens <= 0) return 0;
+    if (hidden <= 0 || top <= 0) return KIPP_ERR_ARG;
+    return kipp_launch(moe_combine_kernel, dim3((unsigned)tokens), dim3(128), 0, (cudaStream_t)stream, 1, y, rows, weight_of,
+                       hidden, top);
+}

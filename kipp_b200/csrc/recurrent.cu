@@ -7,6 +7,9 @@
 //   gated memory     m_t = max(f_t + m_{t-1}, i_t)   (m_0 = 0)
 //                    S_t = e^(f_t + m_{t-1} - m_t) S_{t-1} + e^(i_t - m_t) k_t v_t^T,  n_t likewise with k_t alone
 //                                        o_t = S_t^T q_t / (max(|n_t . q_t|, e^(-m_t)) + 1e-6)
+//   wkv              o_t = (S_{t-1} + diag(u) k_t v_t^T)^T r_t,   S_t = diag(w_t) S_{t-1} + k_t v_t^T
+//                    (the output reads the OLD state; the bonus u counts the current token only;
+//                    w = exp(-exp(w_raw + w_bias)) per head, key channel and token)
 //
 // S is [key dim, value dim].  Retention rotates q and k by the step's (cos, sin)
 // table (pair (i, i + rot/2), the first `rot` dims) and scales k afterwards; its
@@ -65,12 +68,13 @@ struct ScanArgs {
     const float* i_bias; const float* f_bias;
     float gate_cap, q_scale;
     long long slot_stride;                 // floats per slot of `state` (0: heads * dim * v_dim)
+    const float* bonus;                    // wkv: u [heads * dim]
 };
-enum { RETENTION = 0, DELTA_RULE = 1, GATED_MEMORY = 2 };
+enum { RETENTION = 0, DELTA_RULE = 1, GATED_MEMORY = 2, WKV = 3 };
 // vectors per token besides v, extra floats after them, extra value columns
 template <int KIND> struct Rec {
-    static constexpr int NV = KIND == DELTA_RULE ? 5 : 2;
-    static constexpr int XG = KIND == GATED_MEMORY ? 4 : 0;     // (i, f, 0, 0) after the vectors
+    static constexpr int NV = KIND == DELTA_RULE ? 5 : KIND == WKV ? 3 : 2;     // wkv: r, k, w
+    static constexpr int XG = KIND == GATED_MEMORY || KIND == WKV ? 4 : 0;      // (i, f, 0, 0), or wkv's (sum u k r, 0, 0, 0), after the vectors
     static constexpr int XV = KIND == GATED_MEMORY ? 4 : 0;     // value columns (1, 0, 0, 0) after v
 };
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
@@ -108,6 +112,20 @@ recurrent_prepare_kernel(const ScanArgs a, float* __restrict__ vec, int tokens) 
             dst[d] = to_f32(pr[a.q_off + h * D + d]) * a.q_scale;
             dst[D + d] = to_f32(pr[a.k_off + h * D + d]);
         }
+    } else if (KIND == WKV) {
+        const T* w_raw = static_cast<const T*>(a.w_raw);
+        float bonus = 0.f;
+        for (int d = lane; d < D; d += 32) {
+            const int c = h * D + d;
+            const float r = to_f32(pr[a.q_off + c]), k = to_f32(pr[a.k_off + c]);
+            const float wr = to_f32(w_raw[row * a.ld_w + c]) + a.w_bias[c];
+            dst[d] = r;
+            dst[D + d] = k;
+            dst[2 * D + d] = expf(-expf(wr));
+            bonus = fmaf(a.bonus[c] * k, r, bonus);
+        }
+        bonus = warp_sum(bonus);
+        if (lane < XG) dst[NV * D + lane] = lane == 0 ? bonus : 0.f;
     } else if (DELTA) {
         const T* w_raw = static_cast<const T*>(a.w_raw);
         float ss = 0.f;
@@ -216,7 +234,7 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
     float S[CHUNK];
 #pragma unroll
     for (int i = 0; i < CHUNK; ++i) S[i] = (live && row_of(i) < D) ? S_slot[(size_t)row_of(i) * V + col] : 0.f;
-    const float decay = DELTA ? 0.f : a.decay[h];
+    const float decay = DELTA || KIND == WKV ? 0.f : a.decay[h];
 
     load_batch(smem, smem + TB * nvd, recs, rec, nvd, min(TB, n_tok), slice, V, async, VS * P);
     int buf = 0;
@@ -272,18 +290,17 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
                         float qq[4], kk[4], ww[4], aa[4];
                         *reinterpret_cast<float4*>(qq) = *reinterpret_cast<const float4*>(tok + r);
                         *reinterpret_cast<float4*>(kk) = *reinterpret_cast<const float4*>(tok + D + r);
-                        if (DELTA) {
-                            *reinterpret_cast<float4*>(ww) = *reinterpret_cast<const float4*>(tok + 2 * D + r);
-                            *reinterpret_cast<float4*>(aa) = *reinterpret_cast<const float4*>(tok + 3 * D + r);
-                        }
+                        if (DELTA || KIND == WKV) *reinterpret_cast<float4*>(ww) = *reinterpret_cast<const float4*>(tok + 2 * D + r);
+                        if (DELTA) *reinterpret_cast<float4*>(aa) = *reinterpret_cast<const float4*>(tok + 3 * D + r);
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             float s;
                             if (DELTA) s = fmaf(kk[j], v, fmaf(-aa[j], us, ww[j] * S[4 * g + j]));
                             else if (KIND == GATED_MEMORY) s = fmaf(kk[j], tv, keep * S[4 * g + j]);
+                            else if (KIND == WKV) s = fmaf(kk[j], v, ww[j] * S[4 * g + j]);
                             else s = fmaf(kk[j], v, decay * S[4 * g + j]);
+                            o = fmaf(KIND == WKV ? S[4 * g + j] : s, qq[j], o);      // wkv reads the old state
                             S[4 * g + j] = s;
-                            o = fmaf(s, qq[j], o);
                         }
                     }
                 }
@@ -294,14 +311,16 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
                         float s;
                         if (DELTA) s = fmaf(base[D + P * i], v, fmaf(-base[3 * D + P * i], us, base[2 * D + P * i] * S[i]));
                         else if (KIND == GATED_MEMORY) s = fmaf(base[D + P * i], tv, keep * S[i]);
+                        else if (KIND == WKV) s = fmaf(base[D + P * i], v, base[2 * D + P * i] * S[i]);
                         else s = fmaf(base[D + P * i], v, decay * S[i]);
+                        o = fmaf(KIND == WKV ? S[i] : s, base[P * i], o);
                         S[i] = s;
-                        o = fmaf(s, base[P * i], o);
                     }
                 }
             }
 #pragma unroll
             for (int x = P / 2; x > 0; x >>= 1) o += __shfl_xor_sync(0xffffffffu, o, x);
+            if (KIND == WKV) o = fmaf(tok[NV * D], v, o);                   // the current token's own pair, weighted by u
             if (KIND == GATED_MEMORY && col == a.v_dim + 1) o = m_run;      // the column after n's carries m_t to the finish
             if (live && p == 0) o_raw[(size_t)(row0 + t0 + tt) * (a.heads * V) + h * V + col] = o;
         }
@@ -404,6 +423,36 @@ int launch_scan(const ScanArgs& a, int entries, int tokens, float* scratch, cuda
 }
 
 template <typename T>
+__global__ void __launch_bounds__(128)
+token_shift_mix_kernel(T* __restrict__ out, long long out_stride, const T* __restrict__ h, const float* __restrict__ mu,
+                       const float* __restrict__ prev, long long slot_stride, const int* __restrict__ q_start,
+                       const int* __restrict__ entry_of_token, const int* __restrict__ slots, int hidden, int n_mix) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x, e = entry_of_token[t];
+    const bool inside = t > q_start[e];
+    const T* above = h + (size_t)(inside ? t - 1 : t) * hidden;
+    const float* kept = prev + (size_t)slots[e] * slot_stride;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        const float hv = to_f32(h[(size_t)t * hidden + i]);
+        const float d = (inside ? to_f32(above[i]) : kept[i]) - hv;
+        for (int s = 0; s < n_mix; ++s)
+            out[(size_t)s * out_stride + (size_t)t * hidden + i] = from_f32<T>(fmaf(d, mu[(size_t)s * hidden + i], hv));
+    }
+}
+template <typename T>
+__global__ void __launch_bounds__(128)
+token_shift_keep_kernel(float* __restrict__ prev, long long slot_stride, const T* __restrict__ h,
+                        const int* __restrict__ q_start, const int* __restrict__ slots, int hidden) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int e = blockIdx.x, last = q_start[e + 1] - 1;
+    if (last < q_start[e]) return;
+    float* dst = prev + (size_t)slots[e] * slot_stride;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) dst[i] = to_f32(h[(size_t)last * hidden + i]);
+}
+
+template <typename T>
 __global__ void tanh_rows_kernel(T* __restrict__ out, long long ld_out, const T* __restrict__ in, long long ld_in,
                                  int rows, int cols) {
     pdl_launch_dependents();
@@ -417,13 +466,13 @@ __global__ void tanh_rows_kernel(T* __restrict__ out, long long ld_out, const T*
 
 // Whether the scan kernels take a head of these sizes.
 extern "C" int kipp_recurrent_scan_ok(int dim, int v_dim, int kind) {
-    if (dim <= 0 || v_dim <= 0 || dim > 16 * MAX_CHUNK || kind < 0 || kind > 2) return 0;
-    return (((kind == DELTA_RULE ? 5 : 2) * (size_t)dim + 4 + VS) * sizeof(float)) <= 20 * 1024 ? 1 : 0;
+    if (dim <= 0 || v_dim <= 0 || dim > 16 * MAX_CHUNK || kind < 0 || kind > 3) return 0;
+    return (((kind == DELTA_RULE ? 5 : kind == WKV ? 3 : 2) * (size_t)dim + 4 + VS) * sizeof(float)) <= 20 * 1024 ? 1 : 0;
 }
 // float32 values of scratch a scan of `tokens` tokens needs.
 extern "C" long long kipp_recurrent_scratch_floats(int tokens, int heads, int dim, int v_dim, int kind) {
-    const long long x = kind == GATED_MEMORY ? 4 : 0;
-    return (long long)tokens * heads * ((kind == DELTA_RULE ? 5 : 2) * (long long)dim + x + 2 * ((long long)v_dim + x));
+    const long long x = kind == GATED_MEMORY ? 4 : 0, g = kind == WKV ? 4 : 0;
+    return (long long)tokens * heads * ((kind == DELTA_RULE ? 5 : kind == WKV ? 3 : 2) * (long long)dim + x + g + 2 * ((long long)v_dim + x));
 }
 // float32 values of state one request slot of the gated memory holds: S with n's column and its
 // padding, then one running maximum per head and slice of value columns.
@@ -491,6 +540,62 @@ extern "C" int kipp_gated_memory_scan(void* out, long long ld_out, const void* p
     a.slot_stride = kipp_gated_memory_state_floats(heads, dim, v_dim);
     if (dtype == KIPP_DT_F32) return launch_scan<float, GATED_MEMORY>(a, entries, tokens, scratch, (cudaStream_t)stream);
     if (dtype == KIPP_DT_BF16) return launch_scan<bf16, GATED_MEMORY>(a, entries, tokens, scratch, (cudaStream_t)stream);
+    return KIPP_ERR_DTYPE;
+}
+
+// The wkv recurrence (see the head of this file): r, k, v and the output gate [heads, dim] are columns of
+// proj, the decay's pre-activation is w_raw [T, heads * dim]; `bonus` is u [heads * dim].  The state of a
+// slot is `slot_stride` floats of which the first heads * dim * dim are S.
+extern "C" int kipp_wkv_scan(void* out, long long ld_out, const void* proj, long long ld_proj, int dtype, int r_off,
+                             int k_off, int v_off, int g_off, const void* w_raw, long long ld_w, const float* w_bias,
+                             const float* bonus, const float* norm_w, float* state, long long slot_stride,
+                             const int* q_start, const int* slots, int entries, int tokens, int heads, int dim,
+                             float eps, float out_scale, int gate, float* scratch, void* stream) {
+    if (entries <= 0 || tokens <= 0) return 0;
+    if (!kipp_recurrent_scan_ok(dim, dim, WKV) || heads <= 0 || w_bias == nullptr || bonus == nullptr || w_raw == nullptr ||
+        slot_stride < (long long)heads * dim * dim)
+        return KIPP_ERR_ARG;
+    ScanArgs a = {};
+    a.out = out; a.ld_out = ld_out; a.proj = proj; a.ld_proj = ld_proj;
+    a.q_off = r_off; a.k_off = k_off; a.v_off = v_off; a.g_off = g_off;
+    a.w_raw = w_raw; a.ld_w = ld_w; a.w_bias = w_bias; a.bonus = bonus; a.norm_w = norm_w;
+    a.state = state; a.slot_stride = slot_stride; a.q_start = q_start; a.slots = slots;
+    a.heads = heads; a.dim = dim; a.v_dim = dim;
+    a.k_scale = 1.f; a.eps = eps; a.out_scale = out_scale; a.gate = gate;
+    if (dtype == KIPP_DT_F32) return launch_scan<float, WKV>(a, entries, tokens, scratch, (cudaStream_t)stream);
+    if (dtype == KIPP_DT_BF16) return launch_scan<bf16, WKV>(a, entries, tokens, scratch, (cudaStream_t)stream);
+    return KIPP_ERR_DTYPE;
+}
+
+// Token shift: out[s][t, :] = h[t, :] + (h'[t, :] - h[t, :]) * mu[s, :] for s < n_mix, with h' the row of
+// the token before in the same sequence: the row above inside a step's portion, the row the
+// sequence's slot keeps (prev[slot * slot_stride ...], float32, zeros at admission) for the portion's
+// first token.  kipp_token_shift_keep then stores the portion's last row in the slot.
+extern "C" int kipp_token_shift_mix(void* out, long long out_stride, const void* h, const float* mu, const float* prev,
+                                    long long slot_stride, const int* q_start, const int* entry_of_token,
+                                    const int* slots, int dtype, int tokens, int hidden, int n_mix, void* stream) {
+    if (tokens <= 0) return 0;
+    if (hidden <= 0 || n_mix <= 0 || n_mix > 8 || prev == nullptr || mu == nullptr) return KIPP_ERR_ARG;
+    if (dtype == KIPP_DT_F32)
+        return kipp_launch(token_shift_mix_kernel<float>, dim3((unsigned)tokens), dim3(128), 0, (cudaStream_t)stream, 1,
+                           (float*)out, out_stride, (const float*)h, mu, prev, slot_stride, q_start, entry_of_token, slots,
+                           hidden, n_mix);
+    if (dtype == KIPP_DT_BF16)
+        return kipp_launch(token_shift_mix_kernel<bf16>, dim3((unsigned)tokens), dim3(128), 0, (cudaStream_t)stream, 1,
+                           (bf16*)out, out_stride, (const bf16*)h, mu, prev, slot_stride, q_start, entry_of_token, slots,
+                           hidden, n_mix);
+    return KIPP_ERR_DTYPE;
+}
+extern "C" int kipp_token_shift_keep(float* prev, long long slot_stride, const void* h, const int* q_start,
+                                     const int* slots, int dtype, int entries, int hidden, void* stream) {
+    if (entries <= 0) return 0;
+    if (hidden <= 0 || prev == nullptr) return KIPP_ERR_ARG;
+    if (dtype == KIPP_DT_F32)
+        return kipp_launch(token_shift_keep_kernel<float>, dim3((unsigned)entries), dim3(128), 0, (cudaStream_t)stream, 1,
+                           prev, slot_stride, (const float*)h, q_start, slots, hidden);
+    if (dtype == KIPP_DT_BF16)
+        return kipp_launch(token_shift_keep_kernel<bf16>, dim3((unsigned)entries), dim3(128), 0, (cudaStream_t)stream, 1,
+                           prev, slot_stride, (const bf16*)h, q_start, slots, hidden);
     return KIPP_ERR_DTYPE;
 }
 
