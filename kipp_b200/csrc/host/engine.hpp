@@ -18,6 +18,8 @@
 #include "qwen3.hpp"
 #include "venizen.hpp"
 #include "varunex.hpp"
+#include "expert_parts.hpp"
+#include "zasudra.hpp"
 
 namespace kipp {
 
@@ -197,6 +199,7 @@ public:
     // -- what parts and the scheduler reach ---------------------------------------------------------
     PagedCacheView cache_view(const StepMeta& meta, const LayerRun& run, int mixer_slot) const;
     void* state_view(const LayerRun& run, int mixer_slot, size_t* bytes_per_slot) const;
+    void* stage_state(const EmbeddingStage* stage, size_t* bytes_per_slot) const;
     int max_requests() const { return opt_.max_requests; }
     const kipp_engine_options& options() const { return opt_; }
     const ModelPlan& plan() const { return *plan_; }
@@ -251,6 +254,7 @@ private:
     class EngineBinder;
 
     static long long cache_key(int cache, int mixer_slot) { return (long long)cache * 16 + mixer_slot; }
+    static long long stage_key(int stage) { return -1 - (long long)stage; }
 
     void check_memory(const std::vector<TensorSpec>& specs);
     size_t workspace_estimate() const;
@@ -309,6 +313,9 @@ inline PagedCacheView StepContext::cache_view(const LayerRun& run, int mixer_slo
 inline void* StepContext::state_view(const LayerRun& run, int mixer_slot, size_t* bytes_per_slot) const {
     return engine->state_view(run, mixer_slot, bytes_per_slot);
 }
+inline void* StepContext::stage_state(const EmbeddingStage* stage, size_t* bytes_per_slot) const {
+    return engine->stage_state(stage, bytes_per_slot);
+}
 inline int StepContext::max_requests() const { return engine->max_requests(); }
 
 inline void AttentionMixer::forward(StepContext& ctx, const LayerRun& run, int mixer_slot, const void* h,
@@ -317,7 +324,7 @@ inline void AttentionMixer::forward(StepContext& ctx, const LayerRun& run, int m
     const size_t es = ctx.element();
     Ops& ops = *ctx.ops;
     const StepMeta& m = *ctx.meta;
-    const int qkv_cols = q_dim_ + kv_dim_ + vv_dim_;
+    const int qkv_cols = proj_ld_;                                      // the row pitch of the fused projection
     NormFold fold_in, fold_out;
     const PagedCacheView cache = ctx.cache_view(run, mixer_slot);       // pages of this run's cache id
     const int rot = position_->rotary_dim();
@@ -333,12 +340,46 @@ inline void AttentionMixer::forward(StepContext& ctx, const LayerRun& run, int m
         // mixed heads, kept first tokens, value heads of their own size or a scaled output: every
         // head of a query is handled together, scores and weights in float32
         void* qkv = ctx.workspace->buffer("qkv", (size_t)T * qkv_cols * es);
-        ops.gemm(qkv, ctx.dtype, qkv_cols, h, hidden_, w_qkv_, hidden_, dtype_, T, qkv_cols, hidden_, EPI_STORE,
+        ops.gemm(qkv, ctx.dtype, qkv_cols, h, hidden_, w_qkv_, hidden_, dtype_, T, proj_cols_, hidden_, EPI_STORE,
                  fold_input(ctx, fold_in));
         void* q = ctx.workspace->buffer("q", (size_t)T * q_dim_ * es);
         const int write = (run.writes_cache ? 1 : 0) | (ctx.kv_round_bf16 && ctx.dtype == F32 ? 2 : 0);
         AttentionExtras extras;
-        if (segments_) {
+        if (segments_ && !opt_.bias && maps_ == 1) {
+            // the norm over the whole projection, the pairing of the rotation, keys that are also the
+            // values, a mixer without keys of its own: each a property of a run of heads
+            if (opt_.shared_kv == run.writes_cache)
+                fail(KIPP_E_CONFIG, "attention: a mixer with shared_kv runs with writes_cache false, any other with true");
+            HeadSegment seg[3];
+            int n = 0;
+            const float* qw = qk_norm_ ? static_cast<const float*>(q_norm_) : nullptr;
+            const float* kw = qk_norm_ ? static_cast<const float*>(k_norm_) : nullptr;
+            HeadSegment& sq = seg[n++];
+            sq.src_off = 0; sq.heads = heads_; sq.dim = head_dim_; sq.src_stride = head_dim_;
+            sq.norm_w = qw; sq.norm_all = opt_.norm_whole ? 1 : 0;
+            sq.rot = rot; sq.cos_sin = cos_sin; sq.interleaved = opt_.interleaved ? 1 : 0;
+            sq.target = 0; sq.dst = q; sq.ld_dst = q_dim_; sq.dst_stride = head_dim_;
+            if (k_cols_) {
+                HeadSegment& sk = seg[n++];
+                sk.src_off = q_dim_; sk.heads = kv_heads_; sk.dim = head_dim_; sk.src_stride = head_dim_;
+                sk.norm_w = kw; sk.norm_all = opt_.norm_whole ? 1 : 0;
+                sk.rot = rot; sk.cos_sin = cos_sin; sk.interleaved = opt_.interleaved ? 1 : 0;
+                sk.target = 1; sk.heads_per_row = 1;
+                HeadSegment& sv = seg[n++];                              // the values: W_v's rows, or the keys as projected
+                sv.src_off = opt_.values_are_keys ? q_dim_ : q_dim_ + k_cols_;
+                sv.heads = kv_heads_; sv.dim = v_dim_; sv.src_stride = v_dim_;
+                sv.target = 2; sv.heads_per_row = 1;
+            }
+            ops.head_segments(qkv, qkv_cols, ctx.dtype, seg, n, &cache, head_dim_, v_dim_, kv_heads_, m.positions,
+                              m.entry_of_token, T, write, eps_);
+            extras.sink = sink_;
+            extras.chunk = opt_.chunk;
+            if (opt_.head_gate) {
+                extras.gate = static_cast<const char*>(qkv) + (size_t)(q_dim_ + k_cols_ + v_cols_) * es;
+                extras.ld_gate = qkv_cols;
+                extras.gate_off = 0;
+            }
+        } else if (segments_) {
             // biases and score maps: every map of every head is a head of head_dim for the bias and
             // the rotation; the maps of a key head go side by side into one row of the key pages
             HeadSegment seg[3];
@@ -617,6 +658,9 @@ inline void Engine::build_cache() {
             if (auto p = mixers[s]->planner(device_, opt_.own_length_splits != 0)) planners.emplace(p->key(), p);
         }
     }
+    // an embedding stage's state lives beside the mixers' under a key no run can have
+    for (size_t i = 0; i < plan_->embedding.size(); ++i)
+        if (auto ss = plan_->embedding[i].second->state_spec()) state_specs.emplace(stage_key((int)i), *ss);
     for (auto& kv : planners) planners_.push_back(kv.second);
     std::map<PagedKVSpec, std::vector<long long>> by_spec;
     std::vector<PagedKVSpec> spec_order;
@@ -681,6 +725,17 @@ inline void* Engine::state_view(const LayerRun& run, int mixer_slot, size_t* byt
     if (it == states_.end()) fail(KIPP_E_STATE, format("cache %d has no per-request state", run.cache));
     if (bytes_per_slot) *bytes_per_slot = it->second.spec.bytes();
     return it->second.data.get();
+}
+
+inline void* Engine::stage_state(const EmbeddingStage* stage, size_t* bytes_per_slot) const {
+    for (size_t i = 0; i < plan_->embedding.size(); ++i)
+        if (plan_->embedding[i].second.get() == stage) {
+            auto it = states_.find(stage_key((int)i));
+            if (it == states_.end()) break;
+            if (bytes_per_slot) *bytes_per_slot = it->second.spec.bytes();
+            return it->second.data.get();
+        }
+    fail(KIPP_E_STATE, "an embedding stage asked for a state it did not declare");
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -1125,8 +1180,12 @@ inline void Engine::debug_part(const StepEntryView* entries, int n, int run_inde
         return pre;
     };
     ParallelBlock* shared_norm = dynamic_cast<ParallelBlock*>(block);
+    OutputNormBlock* out_norm = dynamic_cast<OutputNormBlock*>(block);
     if (which == "embedding") {
         for (auto& e : plan_->embedding) e.second->forward(ctx, residual);
+    } else if (which == "feed_forward" && out_norm != nullptr) {
+        if (out_norm->feed_forward() == nullptr) fail(KIPP_E_ARGUMENT, "the block has no feed-forward");
+        out_norm->feed_forward()->forward(ctx, input, residual);
     } else if (which == "input_norm" && shared_norm != nullptr) {
         shared_norm->norm()->forward(ctx, residual, output, nullptr, T);
     } else if (which == "feed_forward" && shared_norm != nullptr) {
@@ -1446,7 +1505,7 @@ inline std::string Engine::info_json() {
     Json states = Json::array();
     for (auto& kv : states_) {
         Json o = Json::object();
-        o.set("cache", kv.first / 16);
+        o.set("cache", kv.first < 0 ? (long long)-1 : kv.first / 16);      // -1: an embedding stage's
         o.set("bytes_per_request", (long long)kv.second.spec.bytes());
         states.push(std::move(o));
     }

@@ -119,6 +119,7 @@ public:
     long long launches = 0;                // kernels of this package launched through this object
     bool prefill_tensor_core = true;       // prompt portions on tcgen05 where the sizes allow
     bool mix_tensor_core = true;           // prompt steps of the mixed-head attention on mma.sync where the sizes allow
+    bool moe_tensor_core = true;           // the experts' products on mma.sync where the sizes allow
 
     static constexpr int DECODE_MAX_SPLITS = 32;
     static constexpr int PREFILL_TC_MIN_TOKENS = 64;   // shorter portions waste a 128-row tile
@@ -382,7 +383,7 @@ public:
         static Fn f = kernel_symbol<Fn>("recurrent", "kipp_recurrent_scan_ok");
         return f(dim, v_dim, delta ? 1 : 0) != 0;
     }
-    // kind: 0 retention, 1 delta rule, 2 gated memory
+    // kind: 0 retention, 1 delta rule, 2 gated memory, 3 wkv
     float* recurrent_scratch(int tokens, int heads, int dim, int v_dim, int kind) {
         using Fn = long long (*)(int, int, int, int, int);
         static Fn f = kernel_symbol<Fn>("recurrent", "kipp_recurrent_scratch_floats");
@@ -463,6 +464,112 @@ public:
         using Fn = int (*)(float*, const float*, long long, void*);
         static Fn f = kernel_symbol<Fn>("elementwise", "kipp_add_f32");
         run(f(x, y, n, stream), "add_f32");
+    }
+    // x[t, :] += table[row(t), :] with row = (previous token * mul_prev + token * mul_cur) mod buckets, the
+    // table's extra last row at position 0; the token before a step's first one is last_token[slot * stride].
+    void hashed_pair_add(float* x, const void* table, int table_dtype, const int* ids, const int* positions,
+                         const int* entry_of_token, const int* q_start, const int* slots, const int* last_token,
+                         long long stride, int tokens, int hidden, int vocab, long long buckets, long long mul_prev,
+                         long long mul_cur) {
+        using Fn = int (*)(float*, const void*, int, const int*, const int*, const int*, const int*, const int*, const int*,
+                           long long, int, int, int, long long, long long, long long, int*, void*);
+        static Fn f = kernel_symbol<Fn>("elementwise", "kipp_hashed_pair_add");
+        run(f(x, table, table_dtype, ids, positions, entry_of_token, q_start, slots, last_token, stride, tokens, hidden,
+              vocab, buckets, mul_prev, mul_cur, status, stream),
+            "hashed_pair_add");
+    }
+    // last_token[slots[e] * stride] = the last token entry e brings in this step
+    void keep_last_token(int* last_token, long long stride, const int* ids, const int* q_start, const int* slots,
+                         int entries) {
+        using Fn = int (*)(int*, long long, const int*, const int*, const int*, int, void*);
+        static Fn f = kernel_symbol<Fn>("elementwise", "kipp_keep_last_token");
+        run(f(last_token, stride, ids, q_start, slots, entries, stream), "keep_last_token");
+    }
+    // x[r, :] += mult * y[r, :] * rsqrt(mean(y[r, :]^2) + eps) * w, all float32 (w keeps its storage type)
+    void rmsnorm_scaled_add(float* x, const float* y, const void* w, int w_dtype, int rows, int size, float eps,
+                            float mult) {
+        using Fn = int (*)(float*, const float*, const void*, int, int, int, float, float, void*);
+        static Fn f = kernel_symbol<Fn>("elementwise", "kipp_rmsnorm_scaled_add");
+        run(f(x, y, w, w_dtype, rows, size, eps, mult, stream), "rmsnorm_scaled_add");
+    }
+    void scale_f32(float* x, long long n, float scale) {
+        using Fn = int (*)(float*, long long, float, void*);
+        static Fn f = kernel_symbol<Fn>("elementwise", "kipp_scale_f32");
+        run(f(x, n, scale, stream), "scale_f32");
+    }
+
+    // Token shift (recurrent.cu): out[s][t, :] = h[t, :] + (h'[t, :] - h[t, :]) * mu[s, :], h' the row of the token
+    // before in the same sequence (the slot's kept row for a portion's first token); then the keep.
+    void token_shift_mix(void* out, long long out_stride, const void* h, const float* mu, const float* prev,
+                         long long slot_stride, const int* q_start, const int* entry_of_token, const int* slots,
+                         int dtype, int tokens, int hidden, int n_mix) {
+        using Fn = int (*)(void*, long long, const void*, const float*, const float*, long long, const int*, const int*,
+                           const int*, int, int, int, int, void*);
+        static Fn f = kernel_symbol<Fn>("recurrent", "kipp_token_shift_mix");
+        run(f(out, out_stride, h, mu, prev, slot_stride, q_start, entry_of_token, slots, dtype, tokens, hidden, n_mix,
+              stream),
+            "token_shift_mix");
+    }
+    void token_shift_keep(float* prev, long long slot_stride, const void* h, const int* q_start, const int* slots,
+                          int dtype, int entries, int hidden) {
+        using Fn = int (*)(float*, long long, const void*, const int*, const int*, int, int, int, void*);
+        static Fn f = kernel_symbol<Fn>("recurrent", "kipp_token_shift_keep");
+        run(f(prev, slot_stride, h, q_start, slots, dtype, entries, hidden, stream), "token_shift_keep");
+    }
+    static bool wkv_ok(int dim) {
+        using Fn = int (*)(int, int, int);
+        static Fn f = kernel_symbol<Fn>("recurrent", "kipp_recurrent_scan_ok");
+        return f(dim, dim, 3) != 0;
+    }
+    // o_t = (S_{t-1} + diag(u) k_t v_t^T)^T r_t, S_t = diag(w_t) S_{t-1} + k_t v_t^T with
+    // w = exp(-exp(w_raw + w_bias)) (recurrent.cu); then root-mean-square division, weight, gate.
+    void wkv_scan(void* out, long long ld_out, const void* proj, long long ld_proj, int dtype, int r_off, int k_off,
+                  int v_off, int g_off, const void* w_raw, long long ld_w, const float* w_bias, const float* bonus,
+                  const float* norm_w, float* state, long long slot_stride, const int* q_start, const int* slots,
+                  int entries, int tokens, int heads, int dim, float eps, float out_scale, int gate) {
+        using Fn = int (*)(void*, long long, const void*, long long, int, int, int, int, int, const void*, long long,
+                           const float*, const float*, const float*, float*, long long, const int*, const int*, int, int,
+                           int, int, float, float, int, float*, void*);
+        static Fn f = kernel_symbol<Fn>("recurrent", "kipp_wkv_scan");
+        float* scratch = recurrent_scratch(tokens, heads, dim, dim, 3);
+        run(f(out, ld_out, proj, ld_proj, dtype, r_off, k_off, v_off, g_off, w_raw, ld_w, w_bias, bonus, norm_w, state,
+              slot_stride, q_start, slots, entries, tokens, heads, dim, eps, out_scale, gate, scratch, stream),
+            "wkv_scan", 3);
+    }
+
+    // Routed experts (moe.cu).  route: the `top` largest of z = W_r h + b per token (float32) and the
+    // softmax over them; lists: the (token, choice) pairs sorted by expert and cut into tiles, on the
+    // device; expert_gemm: one product of every tile; combine: y[t] += sum_k weight x row.
+    static int moe_max_tiles(int pairs, int experts) {
+        using Fn = int (*)(int, int);
+        static Fn f = kernel_symbol<Fn>("moe", "kipp_moe_max_tiles");
+        return f(pairs, experts);
+    }
+    void moe_route(int* expert_of, float* weight_of, const void* h, long long ldh, int dtype, const float* router,
+                   const float* bias, int tokens, int hidden, int experts, int top) {
+        using Fn = int (*)(int*, float*, const void*, long long, int, const float*, const float*, int, int, int, int, void*);
+        static Fn f = kernel_symbol<Fn>("moe", "kipp_moe_route");
+        run(f(expert_of, weight_of, h, ldh, dtype, router, bias, tokens, hidden, experts, top, stream), "moe_route");
+    }
+    void moe_lists(int* sorted_pair, int* tile_info, int* n_tiles, const int* expert_of, int pairs, int experts) {
+        using Fn = int (*)(int*, int*, int*, const int*, int, int, void*);
+        static Fn f = kernel_symbol<Fn>("moe", "kipp_moe_lists");
+        run(f(sorted_pair, tile_info, n_tiles, expert_of, pairs, experts, stream), "moe_lists");
+    }
+    void moe_gemm(void* out, int out_dtype, long long ldo, const void* a, long long lda, const void* w, long long w_expert,
+                  int dtype, int N, int K, int top, bool gather, bool scatter, int activation, const int* sorted_pair,
+                  const int* tile_info, const int* n_tiles, int pairs, int experts) {
+        using Fn = int (*)(void*, int, long long, const void*, long long, const void*, long long, int, int, int, int, int,
+                           int, int, const int*, const int*, const int*, int, int, int, void*);
+        static Fn f = kernel_symbol<Fn>("moe", "kipp_moe_gemm");
+        run(f(out, out_dtype, ldo, a, lda, w, w_expert, dtype, N, K, top, gather ? 1 : 0, scatter ? 1 : 0, activation,
+              sorted_pair, tile_info, n_tiles, pairs, experts, moe_tensor_core ? 1 : 0, stream),
+            "moe_gemm", 1, profiling ? format("moe_gemm %d x %d", N, K).c_str() : nullptr);
+    }
+    void moe_combine(float* y, const float* rows, const float* weight_of, int tokens, int hidden, int top) {
+        using Fn = int (*)(float*, const float*, const float*, int, int, int, void*);
+        static Fn f = kernel_symbol<Fn>("moe", "kipp_moe_combine");
+        run(f(y, rows, weight_of, tokens, hidden, top, stream), "moe_combine");
     }
 
     static bool attention_mma_supported(int head_dim, int n_q, int n_kv) {

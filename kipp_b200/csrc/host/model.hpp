@@ -129,6 +129,7 @@ struct RowScale {
 
 class Engine;
 class Norm;
+class EmbeddingStage;
 
 // What a part sees during one step.
 struct StepContext {
@@ -159,6 +160,8 @@ struct StepContext {
     PagedCacheView cache_view(const LayerRun& run, int mixer_slot = 0) const;
     // [max_requests, state bytes] state of this run's cache id; index it with meta->slots.
     void* state_view(const LayerRun& run, int mixer_slot, size_t* bytes_per_slot) const;
+    // [max_requests, state bytes] state of an embedding stage that declared one
+    void* stage_state(const EmbeddingStage* stage, size_t* bytes_per_slot) const;
     int max_requests() const;
 };
 
@@ -236,6 +239,9 @@ public:
 class EmbeddingStage : public Part {
 public:
     virtual void forward(StepContext& ctx, float* x) = 0;
+    // per-request state of the stage (the token before, say): zeroed at admission like a mixer's;
+    // forward finds it with ctx.stage_state(this)
+    virtual std::optional<StateSpec> state_spec() const { return std::nullopt; }
 };
 
 class Head : public Part {
@@ -349,8 +355,8 @@ private:
     std::map<std::string, Architecture> archs_;
 };
 
-void register_builtin_parts();           // parts.hpp, recurrent_parts.hpp, latent_parts.hpp
-void register_builtin_architectures();   // qwen3.hpp, venizen.hpp, varunex.hpp
+void register_builtin_parts();           // parts.hpp, recurrent_parts.hpp, latent_parts.hpp, expert_parts.hpp
+void register_builtin_architectures();   // qwen3.hpp, venizen.hpp, varunex.hpp, zasudra.hpp
 
 inline void ensure_registered() {
     static std::once_flag once;

@@ -37,12 +37,56 @@ private:
     void* weight_ = nullptr;
 };
 
+// A second table addressed by a hash of the token pair, added to the stream: x_t += B[row_t, :] with
+// row_t = (id_{t-1} * mul_prev + id_t * mul_cur) mod buckets and, for the first token of a sequence,
+// the table's extra last row (B has buckets + 1 rows).  The token before a step's first token is
+// per-request state of the stage (one int32 per slot), written after every step.
+class HashedPairEmbedding : public EmbeddingStage {
+public:
+    HashedPairEmbedding(int vocab, int hidden, long long buckets, long long mul_prev, long long mul_cur,
+                        std::string weight_name)
+        : vocab_(vocab), hidden_(hidden), buckets_(buckets), mul_prev_(mul_prev), mul_cur_(mul_cur),
+          name_(std::move(weight_name)) {
+        if (vocab <= 0 || hidden <= 0 || buckets <= 0) fail(KIPP_E_CONFIG, "hashed_pair_embedding: sizes must be positive");
+        if (mul_prev < 0 || mul_cur < 0) fail(KIPP_E_CONFIG, "hashed_pair_embedding: the multipliers must not be negative");
+        // (previous * mul_prev + current * mul_cur) is formed in 64 bits
+        if ((double)vocab * ((double)mul_prev + (double)mul_cur) > 9.0e18)
+            fail(KIPP_E_CONFIG, "hashed_pair_embedding: the multipliers are too large for this vocabulary");
+    }
+    void tensor_specs(const std::string& prefix, std::vector<TensorSpec>& out) const override {
+        TensorSpec s;
+        s.name = prefix + name_;
+        s.shape = {buckets_ + 1, hidden_};
+        out.push_back(s);
+    }
+    std::optional<StateSpec> state_spec() const override { return StateSpec{{1}, I32}; }
+    void bind(Binder& b, const std::string& prefix) override {
+        dtype_ = b.compute_dtype();
+        weight_ = b.shared(prefix + name_, dtype_, buckets_ + 1, hidden_);
+    }
+    void forward(StepContext& ctx, float* x) override {
+        const StepMeta& m = *ctx.meta;
+        int* last = static_cast<int*>(ctx.stage_state(this, nullptr));
+        ctx.ops->hashed_pair_add(x, weight_, dtype_, m.token_ids, m.positions, m.entry_of_token, m.q_start, m.slots, last,
+                                 1, ctx.tokens(), hidden_, vocab_, buckets_, mul_prev_, mul_cur_);
+        ctx.ops->keep_last_token(last, 1, m.token_ids, m.q_start, m.slots, m.shape.entries);
+    }
+
+private:
+    int vocab_, hidden_;
+    long long buckets_, mul_prev_, mul_cur_;
+    int dtype_ = BF16;
+    std::string name_;
+    void* weight_ = nullptr;
+};
+
 // logits = W n for the wanted rows only; W is the tensor `tied_to` when the checkpoint has no
 // head of its own (src/kipp.c:951-956, 3013-3018).
 class OutputHead : public Head {
 public:
-    OutputHead(int vocab, int hidden, std::string tied_to, std::string weight_name = "weight")
-        : vocab_(vocab), hidden_(hidden), tied_to_(std::move(tied_to)), name_(std::move(weight_name)) {
+    OutputHead(int vocab, int hidden, std::string tied_to, std::string weight_name = "weight", double logit_scale = 1.0)
+        : vocab_(vocab), hidden_(hidden), tied_to_(std::move(tied_to)), name_(std::move(weight_name)),
+          scale_((float)logit_scale) {
         if (vocab <= 0 || hidden <= 0) fail(KIPP_E_CONFIG, "output_head: sizes must be positive");
     }
     void tensor_specs(const std::string& prefix, std::vector<TensorSpec>& out) const override {
@@ -64,11 +108,13 @@ public:
     int vocab_size() const override { return vocab_; }
     void forward(StepContext& ctx, const void* h, int n_rows, float* logits) override {
         ctx.ops->gemm(logits, F32, vocab_, h, hidden_, weight_, hidden_, dtype_, n_rows, vocab_, hidden_, EPI_STORE);
+        if (scale_ != 1.0f) ctx.ops->scale_f32(logits, (long long)n_rows * vocab_, scale_);     // logit_scale, in float32
     }
 
 private:
     int vocab_, hidden_, dtype_ = BF16;
     std::string tied_to_, name_;
+    float scale_ = 1.f;
     void* weight_ = nullptr;
 };
 
@@ -464,6 +510,15 @@ inline std::map<std::string, std::string> tensor_names(const Json& j, std::map<s
 // own over the head's values); and, with two maps, their combination into one head
 // (combine_maps: o = a1 - lambda a2 with lambda = exp(lq1 . lk1) - exp(lq2 . lk2) + lambda_init,
 // four vectors of head_dim, then o / sqrt(mean(o^2) + combine_eps) times (1 - lambda_init)).
+//
+// And: the q/k norm over the whole projection row instead of head by head (norm_whole: one mean
+// square over all heads, weights [heads x head_dim] and [kv_heads x head_dim]); a rotation that
+// pairs neighbouring dims (interleaved); blocks of positions as the mask (chunk: a query sees the
+// earlier keys of its own block, counted from position 0 of the sequence); a sink in the softmax's
+// denominator, learned per head or of score 0 (sink); a sigmoid gate per head from a projection of
+// the mixer's input (head_gate); values that are the keys as projected (values_are_keys: no W_v);
+// and a mixer without keys and values of its own that reads what another run wrote (shared_kv:
+// the run order gives it that run's cache id and writes_cache false).
 struct AttentionOptions {
     int value_dim = 0, keep_first = 0;
     bool head_mix = false;
@@ -472,12 +527,20 @@ struct AttentionOptions {
     int score_maps = 1;
     bool combine_maps = false;
     double lambda_init = 0.0, combine_eps = 1e-5;
+    bool norm_whole = false;            // q/k norm over the whole projection row, weights of q's and k's full size
+    bool interleaved = false;           // the rotation pairs dim 2i with dim 2i + 1
+    int chunk = 0;                      // > 0: a query sees the keys j <= p of its own block of `chunk` positions
+    int sink = 0;                       // 0 none, 1 a learned number per head (tensor), 2 a sink of score 0
+    bool head_gate = false;             // head h times sigmoid(W_g h)_h, W_g [heads, hidden]
+    bool values_are_keys = false;       // no W_v: the value of a key is the key as projected (before norm and rotation)
+    bool shared_kv = false;             // no keys and values of its own: the run reads the cache another run wrote
     std::map<std::string, std::string> names = {{"q", "q_proj.weight"}, {"k", "k_proj.weight"}, {"v", "v_proj.weight"},
                                                 {"o", "o_proj.weight"}, {"q_norm", "q_norm.weight"},
                                                 {"k_norm", "k_norm.weight"}, {"head_mix", "head_mix.weight"},
                                                 {"q_bias", "q_proj.bias"}, {"k_bias", "k_proj.bias"},
                                                 {"v_bias", "v_proj.bias"}, {"lq1", "lambda_q1"}, {"lk1", "lambda_k1"},
-                                                {"lq2", "lambda_q2"}, {"lk2", "lambda_k2"}};
+                                                {"lq2", "lambda_q2"}, {"lk2", "lambda_k2"}, {"sink", "sink"},
+                                                {"gate", "g_proj.weight"}};
 };
 
 class AttentionMixer : public Mixer {
@@ -502,12 +565,27 @@ public:
         if (opt_.combine_maps && maps_ != 2) fail(KIPP_E_CONFIG, "attention: combine_maps needs two score maps");
         if (opt_.combine_maps && !(opt_.combine_eps > 0)) fail(KIPP_E_CONFIG, "attention: combine_eps must be positive");
         if (opt_.head_mix && maps_ != 1) fail(KIPP_E_CONFIG, "attention: head_mix and score_maps do not go together");
-        segments_ = opt_.bias || maps_ > 1;
-        if (segments_ && qk_norm_) fail(KIPP_E_CONFIG, "attention: q/k norm with biases or score maps is not supported");
+        const bool more = opt_.norm_whole || opt_.interleaved || opt_.chunk != 0 || opt_.sink != 0 || opt_.head_gate ||
+                          opt_.values_are_keys || opt_.shared_kv;
+        segments_ = opt_.bias || maps_ > 1 || more;
+        if ((opt_.bias || maps_ > 1) && qk_norm_) fail(KIPP_E_CONFIG, "attention: q/k norm with biases or score maps is not supported");
+        if (more && (opt_.bias || maps_ > 1 || opt_.head_mix))
+            fail(KIPP_E_CONFIG, "attention: norm_whole, interleaved, chunk, sink, head_gate, values_are_keys and shared_kv "
+                                "do not go with biases, score maps or head_mix");
+        if (opt_.norm_whole && !qk_norm_) fail(KIPP_E_CONFIG, "attention: norm_whole needs qk_norm_eps");
+        if (opt_.chunk < 0 || (opt_.chunk > 0 && window_ > 0)) fail(KIPP_E_CONFIG, "attention: chunk must not be negative and excludes a window");
+        if (opt_.sink < 0 || opt_.sink > 2) fail(KIPP_E_CONFIG, "attention: sink must be none, learned or unit");
+        if (opt_.values_are_keys && v_dim_ != head_dim) fail(KIPP_E_CONFIG, "attention: values that are the keys have the keys' size");
         q_dim_ = heads * maps_ * head_dim;
         kv_dim_ = kv_heads * maps_ * head_dim;
         vv_dim_ = kv_heads * v_dim_;
         o_dim_ = heads * v_dim_;
+        // columns of the fused projection: q, then k and v where the mixer has its own, then the gate
+        k_cols_ = opt_.shared_kv ? 0 : kv_dim_;
+        v_cols_ = opt_.shared_kv || opt_.values_are_keys ? 0 : vv_dim_;
+        g_cols_ = opt_.head_gate ? heads : 0;
+        proj_cols_ = q_dim_ + k_cols_ + v_cols_ + g_cols_;
+        proj_ld_ = more ? (proj_cols_ + 7) / 8 * 8 : proj_cols_;
         mix_path_ = opt_.head_mix || (window_ > 0 && opt_.keep_first > 0) || v_dim_ != head_dim_ ||
                     opt_.output_scale != 1.0 || segments_;
     }
@@ -520,13 +598,15 @@ public:
             out.push_back(s);
         };
         add("q", {q_dim_, hidden_});
-        add("k", {kv_dim_, hidden_});
-        add("v", {vv_dim_, hidden_});
+        if (k_cols_) add("k", {kv_dim_, hidden_});
+        if (v_cols_) add("v", {vv_dim_, hidden_});
         add("o", {hidden_, o_dim_});
         if (qk_norm_) {
-            add("q_norm", {head_dim_}, "near_one");
-            add("k_norm", {head_dim_}, "near_one");
+            add("q_norm", {opt_.norm_whole ? q_dim_ : head_dim_}, "near_one");
+            if (k_cols_) add("k_norm", {opt_.norm_whole ? kv_dim_ : head_dim_}, "near_one");
         }
+        if (opt_.sink == 1) add("sink", {heads_});
+        if (opt_.head_gate) add("gate", {heads_, hidden_});
         if (opt_.head_mix) add("head_mix", {heads_, heads_}, "near_identity");
         if (opt_.bias) {
             add("q_bias", {q_dim_});
@@ -553,18 +633,30 @@ public:
     void bind(Binder& b, const std::string& p) override {
         dtype_ = b.compute_dtype();
         const size_t es = dtype_size(dtype_);
-        const int64_t rows = q_dim_ + kv_dim_ + vv_dim_;
+        const int64_t rows = proj_cols_;
         const std::string nq = p + opt_.names.at("q"), nk = p + opt_.names.at("k"), nv = p + opt_.names.at("v");
         const std::string no = p + opt_.names.at("o");
-        // one matrix for q, k and v so that one product makes all three
+        // one matrix for q, k and v (and the gate) so that one product makes them all
         w_qkv_ = b.allocate((size_t)rows * hidden_ * es, p + "qkv");
         char* base = static_cast<char*>(w_qkv_);
         b.load(nq, base, dtype_, hidden_, q_dim_, hidden_);
-        b.load(nk, base + (size_t)q_dim_ * hidden_ * es, dtype_, hidden_, kv_dim_, hidden_);
-        b.load(nv, base + (size_t)(q_dim_ + kv_dim_) * hidden_ * es, dtype_, hidden_, vv_dim_, hidden_);
+        if (k_cols_) b.load(nk, base + (size_t)q_dim_ * hidden_ * es, dtype_, hidden_, kv_dim_, hidden_);
+        if (v_cols_) b.load(nv, base + (size_t)(q_dim_ + k_cols_) * hidden_ * es, dtype_, hidden_, vv_dim_, hidden_);
+        if (g_cols_)
+            b.load(p + opt_.names.at("gate"), base + (size_t)(q_dim_ + k_cols_ + v_cols_) * hidden_ * es, dtype_, hidden_,
+                   heads_, hidden_);
         w_o_ = b.allocate((size_t)hidden_ * o_dim_ * es, no);
         b.load(no, w_o_, dtype_, o_dim_, hidden_, o_dim_);
-        if (qk_norm_) {
+        if (qk_norm_ && segments_) {              // the head segments take their norm weights in float32
+            const int64_t nqw = opt_.norm_whole ? q_dim_ : head_dim_, nkw = opt_.norm_whole ? kv_dim_ : head_dim_;
+            norm_dtype_ = F32;
+            q_norm_ = b.allocate((size_t)nqw * sizeof(float), p + opt_.names.at("q_norm"));
+            b.load(p + opt_.names.at("q_norm"), q_norm_, F32, nqw, 1, nqw);
+            if (k_cols_) {
+                k_norm_ = b.allocate((size_t)nkw * sizeof(float), p + opt_.names.at("k_norm"));
+                b.load(p + opt_.names.at("k_norm"), k_norm_, F32, nkw, 1, nkw);
+            }
+        } else if (qk_norm_) {
             const std::string qn = p + opt_.names.at("q_norm"), kn = p + opt_.names.at("k_norm");
             int qd = storage_dtype(b.stored_dtype(qn));
             int kd = storage_dtype(b.stored_dtype(kn));
@@ -589,6 +681,11 @@ public:
             k_bias_ = floats("k_bias", kv_dim_);
             v_bias_ = floats("v_bias", vv_dim_);
         }
+        if (opt_.sink == 1) sink_ = floats("sink", heads_);
+        if (opt_.sink == 2) {                     // a sink of score 0 in every head
+            sink_ = static_cast<float*>(b.allocate((size_t)heads_ * sizeof(float), p + "unit sink"));
+            cuda_check(cudaMemset(sink_, 0, (size_t)heads_ * sizeof(float)), "clearing the unit sink");
+        }
         if (opt_.combine_maps) {
             // lambda is one number for the layer: formed once, in double precision
             double dot[2] = {0.0, 0.0};
@@ -607,8 +704,8 @@ public:
         position_->bind(b, p);
     }
     size_t weight_bytes() const override {
-        size_t n = ((size_t)(q_dim_ + kv_dim_ + vv_dim_) * hidden_ + (size_t)hidden_ * o_dim_) * dtype_size(dtype_);
-        if (qk_norm_) n += 2 * (size_t)head_dim_ * dtype_size(norm_dtype_);
+        size_t n = ((size_t)proj_cols_ * hidden_ + (size_t)hidden_ * o_dim_) * dtype_size(dtype_);
+        if (qk_norm_) n += (opt_.norm_whole ? (size_t)q_dim_ + k_cols_ : 2 * (size_t)head_dim_) * dtype_size(norm_dtype_);
         if (opt_.head_mix) n += (size_t)heads_ * heads_ * sizeof(float);
         if (opt_.bias) n += (size_t)(q_dim_ + kv_dim_ + vv_dim_) * sizeof(float);
         return n;
@@ -629,7 +726,8 @@ private:
     int maps_ = 1;
     float lambda_ = 0.f;
     void *w_qkv_ = nullptr, *w_o_ = nullptr, *q_norm_ = nullptr, *k_norm_ = nullptr;
-    float *head_mix_ = nullptr, *q_bias_ = nullptr, *k_bias_ = nullptr, *v_bias_ = nullptr;
+    float *head_mix_ = nullptr, *q_bias_ = nullptr, *k_bias_ = nullptr, *v_bias_ = nullptr, *sink_ = nullptr;
+    int k_cols_ = 0, v_cols_ = 0, g_cols_ = 0, proj_cols_ = 0, proj_ld_ = 0;
     std::shared_ptr<AttentionPlanner> planner_;
     std::shared_ptr<MixTilePlanner> mix_planner_;
 };
@@ -782,6 +880,84 @@ private:
     std::unique_ptr<Norm> norm_;
     std::unique_ptr<Mixer> mixer_;
     std::unique_ptr<FeedForward> ffn_;
+    std::vector<std::string> names_;
+};
+
+// x += mult * norm1(mixer(x)); x += mult * norm2(ffn(x)): the sublayers read the stream itself (rounded
+// to the compute type), the norm sits on each sublayer's OUTPUT, and `mult` scales what joins the
+// stream.  A sublayer adds its output into a cleared float32 buffer; the norm of that buffer and the
+// addition to the stream are one float32 kernel.  The norms must be plain RMS norms.  A block
+// without a feed-forward (post_norm and ffn null) has the first sublayer only.
+class OutputNormBlock : public Block {
+public:
+    OutputNormBlock(std::unique_ptr<Norm> n1, std::unique_ptr<Mixer> mixer, std::unique_ptr<Norm> n2,
+                    std::unique_ptr<FeedForward> ffn, double mult, std::vector<std::string> names)
+        : n1_(std::move(n1)), mixer_(std::move(mixer)), n2_(std::move(n2)), ffn_(std::move(ffn)), mult_((float)mult),
+          names_(std::move(names)) {
+        if (names_.size() != 4) fail(KIPP_E_CONFIG, "output_norm_block: four name prefixes are needed");
+        if ((n2_ == nullptr) != (ffn_ == nullptr))
+            fail(KIPP_E_CONFIG, "output_norm_block: post_norm and ffn come together or not at all");
+        if (n2_ && n1_->size() != n2_->size()) fail(KIPP_E_CONFIG, "output_norm_block: the two norms differ in size");
+    }
+    void tensor_specs(const std::string& p, std::vector<TensorSpec>& out) const override {
+        n1_->tensor_specs(p + names_[0], out);
+        mixer_->tensor_specs(p + names_[1], out);
+        if (ffn_) {
+            n2_->tensor_specs(p + names_[2], out);
+            ffn_->tensor_specs(p + names_[3], out);
+        }
+    }
+    void bind(Binder& b, const std::string& p) override {
+        n1_->bind(b, p + names_[0]);
+        mixer_->bind(b, p + names_[1]);
+        if (ffn_) {
+            n2_->bind(b, p + names_[2]);
+            ffn_->bind(b, p + names_[3]);
+        }
+        if (!n1_->rms_spec() || (n2_ && !n2_->rms_spec()))
+            fail(KIPP_E_CONFIG, "output_norm_block: the norms on the sublayers' outputs must be RMS norms");
+    }
+    size_t weight_bytes() const override {
+        return n1_->weight_bytes() + mixer_->weight_bytes() + (ffn_ ? n2_->weight_bytes() + ffn_->weight_bytes() : 0);
+    }
+    bool graph_safe() const override {
+        return n1_->graph_safe() && mixer_->graph_safe() && (!ffn_ || (n2_->graph_safe() && ffn_->graph_safe()));
+    }
+    std::vector<Mixer*> mixers() override { return mixer_->parts(); }
+    void forward(StepContext& ctx, const LayerRun& run, float* x) override {
+        const int T = ctx.tokens(), W = n1_->size();
+        // no norm runs before a sublayer here: nothing to fold into the products, nothing pending
+        ctx.input_scale = RowScale{};
+        ctx.pending_norm = nullptr;
+        ctx.emit_for = nullptr;
+        ctx.emitted = false;
+        float* y = ctx.workspace->get<float>("sublayer_output", (size_t)T * W);
+        auto sublayer = [&](const Norm& norm, auto&& run_part) {
+            const void* h = x;                    // 32-bit path: the sublayer reads the stream in place
+            if (ctx.dtype != F32) {
+                void* hc = ctx.workspace->buffer("normed", (size_t)T * W * ctx.element());
+                ctx.ops->convert_rows(hc, ctx.dtype, W, x, F32, W, T, W);
+                h = hc;
+            }
+            cuda_check(cudaMemsetAsync(y, 0, (size_t)T * W * sizeof(float), ctx.stream), "clearing a sublayer's output");
+            run_part(h);
+            const RmsNormSpec spec = *norm.rms_spec();
+            ctx.ops->rmsnorm_scaled_add(x, y, spec.weight, spec.weight_dtype, T, W, spec.eps, mult_);
+        };
+        sublayer(*n1_, [&](const void* h) { mixer_->forward(ctx, run, 0, h, y); });
+        if (ffn_) sublayer(*n2_, [&](const void* h) { ffn_->forward(ctx, h, y); });
+        ctx.emitted = false;
+    }
+    Norm* mixer_norm() { return n1_.get(); }
+    Norm* post_norm() { return n2_.get(); }
+    FeedForward* feed_forward() { return ffn_.get(); }
+
+private:
+    std::unique_ptr<Norm> n1_;
+    std::unique_ptr<Mixer> mixer_;
+    std::unique_ptr<Norm> n2_;
+    std::unique_ptr<FeedForward> ffn_;
+    float mult_;
     std::vector<std::string> names_;
 };
 
@@ -1045,6 +1221,7 @@ inline std::unique_ptr<PositionEncoding> make_position(const Json& j, const Buil
 }
 void register_recurrent_parts(Registry& r);     // recurrent_parts.hpp
 void register_latent_parts(Registry& r);        // latent_parts.hpp
+void register_expert_parts(Registry& r);        // expert_parts.hpp
 
 inline void register_builtin_parts() {
     Registry& r = Registry::get();
@@ -1054,7 +1231,13 @@ inline void register_builtin_parts() {
     });
     r.add_part_kind("output_head", [](const Json& j, const BuildContext&) -> std::unique_ptr<Part> {
         return std::make_unique<OutputHead>((int)j.get("vocab_size").as_int(), (int)j.get("hidden_size").as_int(),
-                                            j.get_string("tied_to", ""), j.get_string("weight_name", "weight"));
+                                            j.get_string("tied_to", ""), j.get_string("weight_name", "weight"),
+                                            j.get_double("logit_scale", 1.0));
+    });
+    r.add_part_kind("hashed_pair_embedding", [](const Json& j, const BuildContext&) -> std::unique_ptr<Part> {
+        return std::make_unique<HashedPairEmbedding>((int)j.get("vocab_size").as_int(), (int)j.get("hidden_size").as_int(),
+                                                     j.get("buckets").as_int(), j.get("mul_prev").as_int(),
+                                                     j.get("mul_cur").as_int(), j.get_string("weight_name", "weight"));
     });
     r.add_part_kind("rmsnorm", [](const Json& j, const BuildContext&) -> std::unique_ptr<Part> {
         return std::make_unique<RMSNorm>((int)j.get("size").as_int(), j.get("eps").as_double(),
@@ -1125,6 +1308,16 @@ inline void register_builtin_parts() {
         options.combine_maps = j.get_bool("combine_maps", false);
         options.lambda_init = j.get_double("lambda_init", 0.0);
         options.combine_eps = j.get_double("combine_eps", 1e-5);
+        options.norm_whole = j.get_bool("norm_whole", false);
+        options.interleaved = j.get_bool("interleaved", false);
+        options.chunk = (int)j.get_int("chunk", 0);
+        const std::string sink = j.get_string("sink", "none");
+        if (sink != "none" && sink != "learned" && sink != "unit")
+            fail(KIPP_E_CONFIG, "attention: sink must be none, learned or unit, not '" + sink + "'");
+        options.sink = sink == "learned" ? 1 : sink == "unit" ? 2 : 0;
+        options.head_gate = j.get_bool("head_gate", false);
+        options.values_are_keys = j.get_bool("values_are_keys", false);
+        options.shared_kv = j.get_bool("shared_kv", false);
         options.names = tensor_names(j, options.names);
         return std::make_unique<AttentionMixer>(
             (int)j.get("hidden_size").as_int(), (int)j.get("num_heads").as_int(), (int)j.get("num_kv_heads").as_int(),
@@ -1148,8 +1341,23 @@ inline void register_builtin_parts() {
             has_ffn ? reg.make_as<Norm>(*n2, ctx, "a norm") : nullptr,
             has_ffn ? reg.make_as<FeedForward>(*ff, ctx, "a feed-forward") : nullptr, names);
     });
+    r.add_part_kind("output_norm_block", [](const Json& j, const BuildContext& ctx) -> std::unique_ptr<Part> {
+        const Registry& reg = Registry::get();
+        std::vector<std::string> names;
+        for (auto& n : j.get("names").items()) names.push_back(n.as_string());
+        const Json* n2 = j.find("post_norm");
+        const Json* ff = j.find("ffn");
+        const bool has_ffn = ff != nullptr && !ff->is_null();
+        if (has_ffn && (n2 == nullptr || n2->is_null())) fail(KIPP_E_CONFIG, "output_norm_block: a feed-forward needs its post_norm");
+        return std::make_unique<OutputNormBlock>(
+            reg.make_as<Norm>(j.get("mixer_norm"), ctx, "a norm"), reg.make_as<Mixer>(j.get("mixer"), ctx, "a mixer"),
+            has_ffn ? reg.make_as<Norm>(*n2, ctx, "a norm") : nullptr,
+            has_ffn ? reg.make_as<FeedForward>(*ff, ctx, "a feed-forward") : nullptr, j.get_double("residual_mult", 1.0),
+            names);
+    });
     register_recurrent_parts(r);
     register_latent_parts(r);
+    register_expert_parts(r);
     r.add_part_kind("external", [](const Json& j, const BuildContext& ctx) -> std::unique_ptr<Part> {
         const std::string role = j.get("role").as_string();
         if (role == "mixer") return std::make_unique<ExternalMixer>(j, ctx);

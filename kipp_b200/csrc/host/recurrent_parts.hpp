@@ -5,6 +5,8 @@
 //   delta_rule    the generalized delta rule: decay and removal rate per head, key channel and token
 //   gated_memory  the matrix memory of the xLSTM: exponential input and forget gates per head and
 //                 token, held stable by a running maximum, with a normalizer vector beside the matrix
+//   wkv           time mixing with a decay per head, key channel and token and a bonus for the current
+//                 token; every projection reads its own mix of the token's input and the one before
 //   parallel      the sum of several mixers that read the same input
 //   polynorm_mlp  W_down act(W_up h), act = c0 N(z) + c1 N(z^2) + c2 N(z^3) + c3
 //
@@ -474,7 +476,155 @@ private:
     float* coef_ = nullptr;
 };
 
+// ---------------------------------------------------------------------------------------------
+// Time mixing with a decay that depends on the token (the wkv recurrence).  With h' the input row of
+// the token before (zeros before the first token of a sequence), each of r, k, v, g, w reads its own
+// mix h + (h' - h) * mu_s.  r, k, v = W_r, W_k, W_v of their mixes [heads, dim]; the gate is
+// gate(W_g mix_g); the decay w = exp(-exp(W_w2 tanh(W_w1 mix_w) + w0)) per head and key channel, bias,
+// both exponentials and the state in float32.  Per head o_t = (S_{t-1} + diag(u) k_t v_t^T)^T r_t, then
+// S_t = diag(w_t) S_{t-1} + k_t v_t^T.  Each head's o divided by its root mean square (eps inside the
+// root), heads concatenated, times the weight `norm`, times the gate, times output_scale, through W_o.
+// Per request slot the state is S [heads, dim, dim] followed by h' [hidden], float32.
+class WkvMixer : public Mixer {
+public:
+    WkvMixer(const Json& j, const BuildContext&) {
+        hidden_ = (int)j.get("hidden_size").as_int();
+        heads_ = (int)j.get("num_heads").as_int();
+        dim_ = (int)j.get("head_dim").as_int();
+        rank_ = (int)j.get_int("decay_rank", 0);      // 0: the width of the bottleneck is read from its tensor
+        eps_ = (float)j.get("eps").as_double();
+        out_scale_ = (float)j.get_double("output_scale", 1.0);
+        gate_ = gate_code(j.get_string("gate", "silu"));
+        names_ = tensor_names(j, {{"r", "r"}, {"k", "k"}, {"v", "v"}, {"g", "g"}, {"w1", "w1"}, {"w2", "w2"},
+                                  {"w_bias", "w0"}, {"bonus", "u"}, {"norm", "norm"}, {"o", "o"}, {"mu_r", "mu.r"},
+                                  {"mu_k", "mu.k"}, {"mu_v", "mu.v"}, {"mu_g", "mu.g"}, {"mu_w", "mu.w"}});
+        if (hidden_ <= 0 || heads_ <= 0 || dim_ <= 0 || rank_ < 0) fail(KIPP_E_CONFIG, "wkv: sizes must be positive");
+        hd_ = heads_ * dim_;
+        hd_ld_ = (hd_ + 7) / 8 * 8;                    // r, k, v and g each start on a 16-byte boundary of the row
+        n_proj_ = gate_ ? 4 : 3;
+        set_rank(rank_);
+    }
+    void set_rank(int rank) {
+        rank_ = rank;
+        rank_ld_ = (rank_ + 7) / 8 * 8;
+    }
+    void tensor_specs(const std::string& p, std::vector<TensorSpec>& out) const override {
+        auto add = [&](const char* role, std::vector<int64_t> shape, const char* init = "normal") {
+            TensorSpec s;
+            s.name = p + names_.at(role);
+            s.shape = std::move(shape);
+            s.init = init;
+            out.push_back(s);
+        };
+        for (const char* mu : {"mu_r", "mu_k", "mu_v", "mu_g", "mu_w"})
+            if (gate_ || std::string(mu) != "mu_g") add(mu, {hidden_});
+        add("r", {hd_, hidden_});
+        add("k", {hd_, hidden_});
+        add("v", {hd_, hidden_});
+        if (gate_) add("g", {hd_, hidden_});
+        add("w1", {rank_ > 0 ? rank_ : -1, hidden_});
+        add("w2", {hd_, rank_ > 0 ? rank_ : -1});
+        add("w_bias", {hd_});
+        add("bonus", {heads_, dim_});
+        add("norm", {hd_}, "near_one");
+        add("o", {hidden_, hd_});
+    }
+    long long state_floats() const { return (long long)heads_ * dim_ * dim_ + hidden_; }
+    std::optional<StateSpec> state_spec() const override { return StateSpec{{state_floats()}, F32}; }
+    void bind(Binder& b, const std::string& p) override {
+        dtype_ = b.compute_dtype();
+        const size_t es = dtype_size(dtype_);
+        if (rank_ == 0) {
+            const std::vector<int64_t> s1 = b.stored_shape(p + names_.at("w1")), s2 = b.stored_shape(p + names_.at("w2"));
+            if (s1.size() != 2 || s2.size() != 2 || s1[0] <= 0 || s1[0] != s2[1])
+                fail(KIPP_E_WEIGHTS, "wkv: " + p + names_.at("w1") + " and " + p + names_.at("w2") +
+                                         " do not agree on the width of the bottleneck");
+            set_rank((int)s1[0]);
+        }
+        // every projection reads a mix of its own, so each is a product of its own
+        const char* roles[4] = {"r", "k", "v", "g"};
+        for (int i = 0; i < n_proj_; ++i) {
+            w_in_[i] = b.allocate((size_t)hd_ * hidden_ * es, p + names_.at(roles[i]));
+            b.load(p + names_.at(roles[i]), w_in_[i], dtype_, hidden_, hd_, hidden_);
+        }
+        w1_ = b.allocate((size_t)rank_ * hidden_ * es, p + names_.at("w1"));
+        b.load(p + names_.at("w1"), w1_, dtype_, hidden_, rank_, hidden_);
+        // rows of W_w2 and W_o padded to a multiple of 8 elements (zeros beyond)
+        w2_ = b.allocate((size_t)hd_ * rank_ld_ * es, p + names_.at("w2"));
+        cuda_check(cudaMemset(w2_, 0, (size_t)hd_ * rank_ld_ * es), "clearing a padded weight");
+        b.load(p + names_.at("w2"), w2_, dtype_, rank_ld_, hd_, rank_);
+        w_o_ = b.allocate((size_t)hidden_ * hd_ld_ * es, p + names_.at("o"));
+        cuda_check(cudaMemset(w_o_, 0, (size_t)hidden_ * hd_ld_ * es), "clearing a padded weight");
+        b.load(p + names_.at("o"), w_o_, dtype_, hd_ld_, hidden_, hd_);
+        // the mixing vectors in the order of the mixes: r, k, v, (g,) w
+        n_mix_ = n_proj_ + 1;
+        mu_ = static_cast<float*>(b.allocate((size_t)n_mix_ * hidden_ * sizeof(float), p + "mu"));
+        const char* mus[5] = {"mu_r", "mu_k", "mu_v", "mu_g", "mu_w"};
+        int row = 0;
+        for (int i = 0; i < 5; ++i) {
+            if (!gate_ && i == 3) continue;
+            b.load(p + names_.at(mus[i]), mu_ + (size_t)row * hidden_, F32, hidden_, 1, hidden_);
+            ++row;
+        }
+        w_bias_ = load_f32(b, p + names_.at("w_bias"), hd_);
+        bonus_ = load_f32(b, p + names_.at("bonus"), hd_);
+        norm_ = load_f32(b, p + names_.at("norm"), hd_);
+        if (!Ops::wkv_ok(dim_)) fail(KIPP_E_UNSUPPORTED, format("wkv: the scan kernel does not take heads of %d x %d", dim_, dim_));
+    }
+    size_t weight_bytes() const override {
+        return ((size_t)n_proj_ * hd_ * hidden_ + (size_t)rank_ * hidden_ + (size_t)hd_ * rank_ + (size_t)hidden_ * hd_) *
+                   dtype_size(dtype_) + ((size_t)3 * hd_ + (size_t)n_mix_ * hidden_) * 4;
+    }
+    void forward(StepContext& ctx, const LayerRun& run, int mixer_slot, const void* h, float* residual) override {
+        const int T = ctx.tokens();
+        const size_t es = ctx.element();
+        Ops& ops = *ctx.ops;
+        const StepMeta& m = *ctx.meta;
+        float* state = static_cast<float*>(ctx.state_view(run, mixer_slot, nullptr));
+        const long long stride = state_floats();
+        float* prev = state + (size_t)heads_ * dim_ * dim_;          // h' of slot 0; the slots are `stride` apart
+        // the mixes, one [T, hidden] after another, then the row the next step's first token will want
+        char* mixes = static_cast<char*>(ctx.workspace->buffer("wkv_mixes", (size_t)n_mix_ * T * hidden_ * es));
+        const size_t mix_bytes = (size_t)T * hidden_ * es;
+        ops.token_shift_mix(mixes, (long long)T * hidden_, h, mu_, prev, stride, m.q_start, m.entry_of_token, m.slots,
+                            ctx.dtype, T, hidden_, n_mix_);
+        ops.token_shift_keep(prev, stride, h, m.q_start, m.slots, ctx.dtype, m.shape.entries, hidden_);
+        const int ld = n_proj_ * hd_ld_;
+        char* proj = static_cast<char*>(ctx.workspace->buffer("wkv_proj", (size_t)T * ld * es));
+        for (int i = 0; i < n_proj_; ++i)
+            ops.gemm(proj + (size_t)i * hd_ld_ * es, ctx.dtype, ld, mixes + (size_t)i * mix_bytes, hidden_, w_in_[i], hidden_,
+                     dtype_, T, hd_, hidden_, EPI_STORE);
+        // the decay: the bottleneck with its tanh, then its second product; bias and both exponentials
+        // are the scan kernel's, in float32
+        void* low = ctx.workspace->buffer("wkv_low_rank", (size_t)T * rank_ld_ * es);
+        if (rank_ld_ != rank_) cuda_check(cudaMemsetAsync(low, 0, (size_t)T * rank_ld_ * es, ctx.stream), "clearing the bottleneck");
+        void* low_raw = ctx.workspace->buffer("wkv_low_rank_raw", (size_t)T * rank_ld_ * es);
+        ops.gemm(low_raw, ctx.dtype, rank_ld_, mixes + (size_t)n_proj_ * mix_bytes, hidden_, w1_, hidden_, dtype_, T, rank_,
+                 hidden_, EPI_STORE);
+        ops.tanh_rows(low, rank_ld_, low_raw, rank_ld_, ctx.dtype, T, rank_);
+        void* w_raw = ctx.workspace->buffer("wkv_decay", (size_t)T * hd_ld_ * es);
+        ops.gemm(w_raw, ctx.dtype, hd_ld_, low, rank_ld_, w2_, rank_ld_, dtype_, T, hd_, rank_ld_, EPI_STORE);
+        void* gated = ctx.workspace->buffer("wkv_out", (size_t)T * hd_ld_ * es);
+        if (hd_ld_ != hd_) cuda_check(cudaMemsetAsync(gated, 0, (size_t)T * hd_ld_ * es, ctx.stream), "clearing the padding");
+        ops.wkv_scan(gated, hd_ld_, proj, ld, ctx.dtype, 0, hd_ld_, 2 * hd_ld_, 3 * hd_ld_, w_raw, hd_ld_, w_bias_, bonus_,
+                     norm_, state, stride, m.q_start, m.slots, m.shape.entries, T, heads_, dim_, eps_, out_scale_, gate_);
+        ops.gemm(residual, F32, hidden_, gated, hd_ld_, w_o_, hd_ld_, dtype_, T, hidden_, hd_ld_, EPI_ADD);
+    }
+
+private:
+    int hidden_ = 0, heads_ = 0, dim_ = 0, rank_ = 0, rank_ld_ = 0, hd_ = 0, hd_ld_ = 0, n_proj_ = 4, n_mix_ = 5, gate_ = 1,
+        dtype_ = BF16;
+    float eps_ = 0.f, out_scale_ = 1.f;
+    std::map<std::string, std::string> names_;
+    void* w_in_[4] = {nullptr, nullptr, nullptr, nullptr};
+    void *w1_ = nullptr, *w2_ = nullptr, *w_o_ = nullptr;
+    float *mu_ = nullptr, *w_bias_ = nullptr, *bonus_ = nullptr, *norm_ = nullptr;
+};
+
 inline void register_recurrent_parts(Registry& r) {
+    r.add_part_kind("wkv", [](const Json& j, const BuildContext& ctx) -> std::unique_ptr<Part> {
+        return std::make_unique<WkvMixer>(j, ctx);
+    });
     r.add_part_kind("retention", [](const Json& j, const BuildContext& ctx) -> std::unique_ptr<Part> {
         return std::make_unique<RetentionMixer>(j, ctx);
     });
