@@ -155,6 +155,15 @@ def route(w: dict, p: str, r: dict, h: torch.Tensor):
     return idx, torch.softmax(val, -1)
 
 
+def route_margin(w: dict, p: str, r: dict, h: torch.Tensor) -> torch.Tensor:
+    """[T]: by how much the last chosen logit beats the best one left out (inf when every
+    expert is chosen).  A small margin is a close call that rounding may turn."""
+    z = (h @ w[p + "router"].T + w[p + "router.b"]).sort(-1, descending=True).values
+    if r["top"] >= z.shape[1]:
+        return torch.full((h.shape[0],), math.inf, dtype=F64)
+    return z[:, r["top"] - 1] - z[:, r["top"]]
+
+
 def expert_mixture(w: dict, p: str, mlp: dict, h: torch.Tensor) -> torch.Tensor:
     idx, wt = route(w, p, mlp["router"], h)
     out = torch.zeros(h.shape[0], w[p + "e0.down"].shape[0], dtype=F64)
@@ -165,8 +174,10 @@ def expert_mixture(w: dict, p: str, mlp: dict, h: torch.Tensor) -> torch.Tensor:
     return out
 
 
-def forward(cfg: dict, weights: dict, tokens: list, streams: list | None = None) -> torch.Tensor:
-    """[T, vocab] logits of one whole sequence; ``streams`` collects x after every layer."""
+def forward(cfg: dict, weights: dict, tokens: list, streams: list | None = None,
+            margins: list | None = None) -> torch.Tensor:
+    """[T, vocab] logits of one whole sequence; ``streams`` collects x after every layer,
+    ``margins`` every router's margin [T]."""
     w = {k: (v.to(F64) if v.is_floating_point() else v) for k, v in weights.items()}
     eps, mult = cfg["norm"]["eps"], cfg.get("residual_mult", 1.0)
     x = embed(cfg, w, tokens)
@@ -181,6 +192,8 @@ def forward(cfg: dict, weights: dict, tokens: list, streams: list | None = None)
             y = attention(w, p + "mix.", mx, kind, x, eps, *kept[i])
         x = x + mult * rms_divide(y, eps) * w[p + "norm1"]
         if layer.get("mlp"):
+            if margins is not None:
+                margins.append(route_margin(w, p + "mlp.", layer["mlp"]["router"], x))
             x = x + mult * rms_divide(expert_mixture(w, p + "mlp.", layer["mlp"], x), eps) * w[p + "norm2"]
         if streams is not None:
             streams.append(x.clone())
