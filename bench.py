@@ -169,6 +169,25 @@ def varunex_of(size: str, vocab: int = 32000) -> dict:
             "layers": [order[i % 4] for i in range(layers)]}
 
 
+def zasudra_of(size: str, vocab: int = 32000) -> dict:
+    """The design's mixers in turn (attention in blocks of positions whose values are its keys, the
+    wkv recurrence with heads of 64, gated causal attention with a sink of score 0, and one that
+    reads that layer's keys and values), each beside sixteen experts of which a token takes four:
+    four experts of a quarter of the dense width do the work of one dense feed-forward."""
+    width, heads, kv, dim, ff, layers = DESIGN_SIZES[size]
+    mlp = {"kind": "moe", "expert": {"ff": ff // 4}, "router": {"experts": 16, "top": 4}}
+    blocks = {"type": "attention",
+              "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "mask": {"size": DESIGN_WINDOW},
+                        "rot": {"base": 1e4, "dims": dim // 2}, "scale": dim ** -0.5}, "mlp": mlp}
+    wkv = {"type": "wkv", "mixer": {"heads": width // 64, "dim": 64, "decay_rank": 64}, "mlp": mlp}
+    gated = {"type": "attention_2", "mixer": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5}, "mlp": mlp}
+    borrows = {"type": "attention_2", "mixer": dict(gated["mixer"], kv_from=2), "mlp": mlp}
+    order = [blocks, wkv, gated, borrows]
+    return {"architecture": "Zasudra", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+            "logit_scale": 0.5, "embedding": {"bigram": {"buckets": 65521, "mul_prev": 8191, "mul_cur": 131}},
+            "layers": [order[i % 4] for i in range(layers)]}
+
+
 def qwen3_of(size: str, vocab: int = 32000) -> dict:
     width, heads, kv, dim, ff, layers = DESIGN_SIZES[size]
     return dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=vocab, hidden_size=width,
@@ -187,7 +206,8 @@ def compare_designs(args) -> int:
     from kipp_b200.engine import Engine, StepEntry
     pk, pk_src = peaks()
     T, B, ctx = args.designs_prompt, args.batch, args.designs_prompt
-    families = {"venizen": [("venizen", venizen_of)], "varunex": [("varunex", varunex_of), ("venizen", venizen_of)]}
+    families = {"venizen": [("venizen", venizen_of)], "varunex": [("varunex", varunex_of), ("venizen", venizen_of)],
+                "zasudra": [("zasudra", zasudra_of), ("venizen", venizen_of)]}
     designs = families[args.design_family] + [("qwen3", qwen3_of)]
     out = {"metric": "prefill and decode tokens/s, " + " and ".join(d.capitalize() for d, _ in designs[:-1]) +
                      " beside Qwen3 at equal layer sizes", "dtype": "bf16",
@@ -274,8 +294,9 @@ def main() -> int:
                     help="instead of the default workload: a design (--design-family) beside Qwen3 at equal layer sizes, "
                          f"a list of {','.join(DESIGN_SIZES)} (prefill and decode tokens/s, time per kernel)")
     ap.add_argument("--designs-prompt", type=int, default=2048, help="prompt and decode context of --designs")
-    ap.add_argument("--design-family", default="venizen", choices=["venizen", "varunex"],
-                    help="the design --designs measures: venizen, or varunex (with Venizen, its closest relative, beside it)")
+    ap.add_argument("--design-family", default="venizen", choices=["venizen", "varunex", "zasudra"],
+                    help="the design --designs measures: venizen, or varunex or zasudra (with Venizen, their closest "
+                         "relative, beside it)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)

@@ -292,6 +292,12 @@ struct Params {
     const float* ssq_in; int ssq_in_slots;
     float inv_n, eps;
     kipp_gemm_head_sink heads;   // the HEADS form of the pair kernel only
+    // Grouped form of the one-CTA-per-tile prompt kernel (both null otherwise): token tile i (128 rows
+    // of X, every group's rows padded to whole tiles) meets the weights of group group_of_tile[i],
+    // which are rows [g * features, (g + 1) * features) of W; *group_tiles token tiles are in use.
+    // Both lie in device memory and may come from the kernel before this one.
+    const int* group_of_tile;
+    const int* group_tiles;
 };
 
 // What the next norm needs of a new residual value r of token t, feature f (see Params): called
@@ -411,7 +417,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
     const int total_kb = (p.K + TILE_K - 1) / TILE_K;
     const int kb_begin = split * p.k_blocks_per_split;
     const int kb_end = min(total_kb, kb_begin + p.k_blocks_per_split);
-    const int n_kb = max(0, kb_end - kb_begin);
+    int n_kb = max(0, kb_end - kb_begin);
+    int w0 = f0;                                   // first row of W of this CTA's features
+    if (p.group_of_tile != nullptr) {
+        // grouped: token tile blockIdx.x meets its group's rows of W; a tile that is not in use
+        // has no K blocks (its rows, which nobody reads, become zeros).  The lists come from an
+        // earlier kernel, so every role waits for it first.
+        pdl_wait();
+        if ((int)blockIdx.x < *p.group_tiles) w0 = f0 + p.group_of_tile[blockIdx.x] * p.features;
+        else n_kb = 0;
+    }
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
@@ -436,7 +451,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 for (int i = 0; i < ahead; ++i) {
                     uint8_t* wt = tiles + (size_t)i * C::STAGE_BYTES;
                     mbar_expect_tx(&full[i], C::STAGE_BYTES);
-                    tma_load_2d(wt, &map_w, &full[i], (kb_begin + i) * TILE_K, f0);
+                    tma_load_2d(wt, &map_w, &full[i], (kb_begin + i) * TILE_K, w0);
                 }
             }
             __syncwarp();
@@ -457,7 +472,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 const int k = (kb_begin + i) * TILE_K;
                 if (elect_one()) {
                     mbar_expect_tx(&full[s], C::STAGE_BYTES);
-                    tma_load_2d(wt, &map_w, &full[s], k, f0);
+                    tma_load_2d(wt, &map_w, &full[s], k, w0);
                     tma_load_2d(xt, &map_x, &full[s], k, t0);
                 }
                 __syncwarp();
@@ -490,7 +505,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 }
                 __syncwarp();
             }
-            if (ok && elect_one()) umma_commit(acc_ready);
+            if (ok && n_kb > 0 && elect_one()) umma_commit(acc_ready);   // nobody waits where there was no K block
             __syncwarp();
         }
     } else {
@@ -968,7 +983,12 @@ gemm_tc_tokm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
     pdl_launch_dependents();
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_kb = (p.K + TILE_K - 1) / TILE_K;
-    const int m_tiles = (p.tokens + UMMA_M - 1) / UMMA_M;
+    int m_tiles = (p.tokens + UMMA_M - 1) / UMMA_M;
+    if (p.group_of_tile != nullptr) {
+        // the lists come from an earlier kernel: every role waits for it before it counts the tiles
+        pdl_wait();
+        m_tiles = max(0, min(m_tiles, *p.group_tiles));
+    }
     const int n_tiles = (p.features + TILE_N - 1) / TILE_N;
     const int total_tiles = m_tiles * n_tiles;
 
@@ -993,7 +1013,9 @@ gemm_tc_tokm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             const int first = blockIdx.x;
             const int ahead = min(n_kb, C::STAGES);
             {
-                const int t0 = (first % m_tiles) * UMMA_M, f0 = (first / m_tiles) * TILE_N;
+                const int t0 = (first % m_tiles) * UMMA_M;
+                const int f0 = (first / m_tiles) * TILE_N +
+                               (p.group_of_tile != nullptr ? p.group_of_tile[first % m_tiles] * p.features : 0);
                 for (int i = 0; i < ahead; ++i) {
                     mbar_expect_tx(&full[i], C::STAGE_BYTES);
                     tma_load_2d(tiles + (size_t)i * C::STAGE_BYTES + C::X_BYTES, &map_w, &full[i], i * TILE_K, f0);
@@ -1005,7 +1027,9 @@ gemm_tc_tokm_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_cons
             int it = ahead;                                 // K blocks issued so far, over all tiles
             bool ok = true;
             for (int tile = first; tile < total_tiles && ok; tile += gridDim.x) {
-                const int t0 = (tile % m_tiles) * UMMA_M, f0 = (tile / m_tiles) * TILE_N;
+                const int t0 = (tile % m_tiles) * UMMA_M;
+                const int f0 = (tile / m_tiles) * TILE_N +
+                               (p.group_of_tile != nullptr ? p.group_of_tile[tile % m_tiles] * p.features : 0);
                 for (int i = (tile == first ? ahead : 0); i < n_kb; ++i, ++it) {
                     const int s = it % C::STAGES;
                     if (it >= C::STAGES && !mbar_wait(&empty[s], ((it / C::STAGES) & 1) ^ 1, abort_flag)) {
@@ -1688,3 +1712,56 @@ int gemm_tc_run(void* C, int out_dtype, const void* X, const void* W, int tokens
     }
 }
 }  // namespace
+
+// Grouped product on the persistent prompt kernel: the rows of X are sorted by group and every
+// group's rows are padded to whole tiles of 128 (kipp_gemm_tc_group_rows), so that a tile meets ONE
+// group's weights.  W holds the groups' matrices one after another, [groups * features, K].
+//   C[r, f] = act(sum_k X[r, k] * W[group_of_tile[r / 128] * features + f, k])   for r < 128 * *group_tiles
+// group_of_tile [rows / 128] and group_tiles [1] lie in device memory (the kernel before may write
+// them).  A row of C depends on its own row of X alone; what the padding rows hold does not matter.
+extern "C" int kipp_gemm_tc_group_rows() { return UMMA_M; }
+// The few-token kernel takes the same lists with tiles of 16 rows (`tile_rows` 16 below): a CTA per
+// token tile and 128 features streams its group's weight rows once.
+extern "C" int kipp_gemm_tc_group_rows_few() { return 16; }
+
+extern "C" int kipp_gemm_tc_grouped(void* C, int out_dtype, const void* X, const void* W, int rows, int features, int K,
+                                    long long ldx, long long ldc, int groups, int epilogue, const int* group_of_tile,
+                                    const int* group_tiles, int tile_rows, int* status, void* stream) {
+    if (rows <= 0 || features <= 0) return 0;
+    if (K <= 0 || groups <= 0 || (tile_rows != UMMA_M && tile_rows != 16) || rows % tile_rows ||
+        group_of_tile == nullptr || group_tiles == nullptr)
+        return KIPP_ERR_ARG;
+    if ((ldx % 8) || (K % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return -3;
+    if ((epilogue & 0xff) != EPI_STORE || (epilogue >> 8) > 4 || epilogue < 0) return KIPP_ERR_ARG;
+    if (out_dtype != KIPP_DT_F32 && out_dtype != KIPP_DT_BF16) return KIPP_ERR_DTYPE;
+    if ((long long)groups * features > 0x7fffffffLL) return KIPP_ERR_ARG;
+    if (tile_rows == 16) {
+        CUtensorMap mw, mx;
+        int rc = make_map(&mw, W, groups * features, K, K, 128);
+        if (rc) return rc;
+        rc = make_map(&mx, X, rows, K, ldx, 16);
+        if (rc) return rc;
+        Params p = {};
+        p.C = C; p.out_dtype = out_dtype; p.epilogue = epilogue;
+        p.tokens = rows; p.features = features; p.K = K; p.ldc = ldc;
+        p.k_blocks_per_split = (K + TILE_K - 1) / TILE_K; p.splits = 1; p.status = status;
+        p.group_of_tile = group_of_tile; p.group_tiles = group_tiles;
+        dim3 grid(rows / 16, (features + 127) / 128, 1);
+        if (grid.y > 65535) return KIPP_ERR_ARG;
+        return launch<16, 128>(mw, mx, p, grid, (cudaStream_t)stream);
+    }
+    const int tile_n = pick_tile_n(rows, features, false);
+    CUtensorMap mw, mx;
+    int rc = make_map(&mw, W, groups * features, K, K, tile_n);
+    if (rc) return rc;
+    rc = make_map(&mx, X, rows, K, ldx, UMMA_M);
+    if (rc) return rc;
+    Params p = {};
+    p.C = C; p.out_dtype = out_dtype; p.epilogue = epilogue;
+    p.tokens = rows; p.features = features; p.K = K; p.ldc = ldc;
+    p.k_blocks_per_split = (K + TILE_K - 1) / TILE_K; p.splits = 1; p.status = status;
+    p.group_of_tile = group_of_tile; p.group_tiles = group_tiles;
+    const long long total = (long long)(rows / UMMA_M) * ((features + tile_n - 1) / tile_n);
+    if (total > 0x7fffffffLL) return KIPP_ERR_ARG;
+    return launch_tokm_n<false>(tile_n, mw, mx, mw, p, (int)total, (cudaStream_t)stream);
+}

@@ -66,6 +66,30 @@ public:
     void forward(StepContext& ctx, const void* h, float* residual) override {
         const int T = ctx.tokens(), pairs = T * top_;
         Ops& ops = *ctx.ops;
+        if (ops.moe_tensor_core && ctx.dtype == dtype_ && Ops::moe_grouped_ok(dtype_, hidden_, inter_)) {
+            // bfloat16: the pairs' rows sorted by expert and padded to whole tiles, each projection
+            // ONE grouped product on the tcgen05 kernels (tiles of 128 rows for prompt-sized steps,
+            // of 16 for few tokens)
+            const int tile = Ops::grouped_tile_rows(T, pairs, experts_);
+            const int cap = Ops::moe_max_padded_tiles(pairs, experts_, tile), rows_cap = cap * tile;
+            int* expert_of = ctx.workspace->get<int>("moe_expert_of", (size_t)pairs);
+            float* weight_of = ctx.workspace->get<float>("moe_weight_of", (size_t)pairs);
+            int* place = ctx.workspace->get<int>("moe_place_of_pair", (size_t)pairs);
+            int* tile_expert = ctx.workspace->get<int>("moe_expert_of_tile", (size_t)cap + 1);
+            int* n_tiles = tile_expert + cap;
+            void* in = ctx.workspace->buffer("moe_input_rows", (size_t)rows_cap * hidden_ * ctx.element());
+            void* act = ctx.workspace->buffer("moe_hidden_rows", (size_t)rows_cap * inter_ * ctx.element());
+            float* rows = ctx.workspace->get<float>("moe_output_rows", (size_t)rows_cap * hidden_);
+            ops.moe_route(expert_of, weight_of, h, hidden_, ctx.dtype, router_, bias_, T, hidden_, experts_, top_);
+            ops.moe_padded_lists(place, tile_expert, n_tiles, expert_of, pairs, experts_, tile);
+            ops.moe_gather_rows(in, h, hidden_, place, pairs, top_, hidden_);
+            ops.gemm_grouped(act, ctx.dtype, inter_, in, hidden_, w_up_, rows_cap, inter_, hidden_, experts_, act_, tile_expert,
+                             n_tiles, tile);
+            ops.gemm_grouped(rows, F32, hidden_, act, inter_, w_down_, rows_cap, hidden_, inter_, experts_, -1, tile_expert,
+                             n_tiles, tile);
+            ops.moe_combine(residual, rows, weight_of, T, hidden_, top_, place);
+            return;
+        }
         const int max_tiles = Ops::moe_max_tiles(pairs, experts_);
         int* expert_of = ctx.workspace->get<int>("moe_expert_of", (size_t)pairs);
         float* weight_of = ctx.workspace->get<float>("moe_weight_of", (size_t)pairs);

@@ -119,7 +119,7 @@ public:
     long long launches = 0;                // kernels of this package launched through this object
     bool prefill_tensor_core = true;       // prompt portions on tcgen05 where the sizes allow
     bool mix_tensor_core = true;           // prompt steps of the mixed-head attention on mma.sync where the sizes allow
-    bool moe_tensor_core = true;           // the experts' products on mma.sync where the sizes allow
+    bool moe_tensor_core = true;           // the experts' products on the tensor cores where the sizes allow
 
     static constexpr int DECODE_MAX_SPLITS = 32;
     static constexpr int PREFILL_TC_MIN_TOKENS = 64;   // shorter portions waste a 128-row tile
@@ -566,10 +566,51 @@ public:
               sorted_pair, tile_info, n_tiles, pairs, experts, moe_tensor_core ? 1 : 0, stream),
             "moe_gemm", 1, profiling ? format("moe_gemm %d x %d", N, K).c_str() : nullptr);
     }
-    void moe_combine(float* y, const float* rows, const float* weight_of, int tokens, int hidden, int top) {
-        using Fn = int (*)(float*, const float*, const float*, int, int, int, void*);
+    void moe_combine(float* y, const float* rows, const float* weight_of, int tokens, int hidden, int top,
+                     const int* place_of_pair = nullptr) {
+        using Fn = int (*)(float*, const float*, const float*, int, int, int, const int*, void*);
         static Fn f = kernel_symbol<Fn>("moe", "kipp_moe_combine");
-        run(f(y, rows, weight_of, tokens, hidden, top, stream), "moe_combine");
+        run(f(y, rows, weight_of, tokens, hidden, top, place_of_pair, stream), "moe_combine");
+    }
+    // The grouped road of prompt-sized steps: the pairs' rows sorted by expert, every expert's rows
+    // padded to whole tiles of the tcgen05 prompt kernel, and one grouped product per projection.
+    // rows of a tile: those of the prompt kernel where a step brings many rows per expert, else
+    // those of the few-token kernel, which streams an expert's weights once per tile of 16 rows
+    static int grouped_tile_rows(int tokens, int pairs, int experts) {
+        using Fn = int (*)();
+        static Fn many = kernel_symbol<Fn>("gemm_tc", "kipp_gemm_tc_group_rows");
+        static Fn few = kernel_symbol<Fn>("gemm_tc", "kipp_gemm_tc_group_rows_few");
+        return tokens >= 256 && pairs >= 64LL * experts ? many() : few();
+    }
+    static bool moe_grouped_ok(int dtype, int hidden, int inter) {
+        return dtype == BF16 && hidden % 8 == 0 && inter % 8 == 0;
+    }
+    static int moe_max_padded_tiles(int pairs, int experts, int tile_rows) {
+        using Fn = int (*)(int, int, int);
+        static Fn f = kernel_symbol<Fn>("moe", "kipp_moe_max_padded_tiles");
+        return f(pairs, experts, tile_rows);
+    }
+    void moe_padded_lists(int* place_of_pair, int* expert_of_tile, int* n_tiles, const int* expert_of, int pairs,
+                          int experts, int tile_rows) {
+        using Fn = int (*)(int*, int*, int*, const int*, int, int, int, void*);
+        static Fn f = kernel_symbol<Fn>("moe", "kipp_moe_padded_lists");
+        run(f(place_of_pair, expert_of_tile, n_tiles, expert_of, pairs, experts, tile_rows, stream), "moe_lists");
+    }
+    void moe_gather_rows(void* dst, const void* src, long long ld_src, const int* place_of_pair, int pairs, int top,
+                         int hidden) {
+        using Fn = int (*)(void*, const void*, long long, const int*, int, int, int, void*);
+        static Fn f = kernel_symbol<Fn>("moe", "kipp_moe_gather_rows");
+        run(f(dst, src, ld_src, place_of_pair, pairs, top, hidden, stream), "moe_gather_rows");
+    }
+    // out[r, :] = act(a[r, :] x w[expert_of_tile[r / tile]]^T) for the rows of the tiles in use
+    void gemm_grouped(void* out, int out_dtype, long long ldc, const void* a, long long lda, const void* w, int rows, int N,
+                      int K, int groups, int activation, const int* expert_of_tile, const int* n_tiles, int tile_rows) {
+        using Fn = int (*)(void*, int, const void*, const void*, int, int, int, long long, long long, int, int, const int*,
+                           const int*, int, int*, void*);
+        static Fn f = kernel_symbol<Fn>("gemm_tc", "kipp_gemm_tc_grouped");
+        const int code = (int)EPI_STORE | (activation >= 0 ? (activation + 1) << 8 : 0);
+        run(f(out, out_dtype, a, w, rows, N, K, lda, ldc, groups, code, expert_of_tile, n_tiles, tile_rows, status, stream),
+            "gemm_tc_grouped", 1, profiling ? format("gemm_tc_grouped %d x %d", N, K).c_str() : nullptr);
     }
 
     static bool attention_mma_supported(int head_dim, int n_q, int n_kv) {

@@ -10,6 +10,11 @@
 //             times the expert's down projection into one float32 row per pair;
 //   combine   y[t] += sum over the token's choices, in the order of their rank, of weight x row.
 //
+// Prompt-sized steps in bfloat16 take another road for the two products: the pairs' input rows are
+// copied into a buffer sorted by expert in which every expert's rows are padded to whole tiles of 128
+// (padded lists, gather), and both products run as ONE grouped product each on the tcgen05 prompt
+// kernel of gemm_tc.cu, whose token tiles then meet one expert's weights each.
+//
 // A pair's row is computed from its own token alone, in an order of sums that depends on the
 // sizes only: the result does not depend on which other tokens share its tile.  The products run
 // on the tensor cores (mma.sync m16n8k16, bfloat16 in, float32 sums) or, in 32-bit and for sizes
@@ -21,55 +26,101 @@
 namespace {
 constexpr int BM = 64, BN = 64, BK = 16, TM = 4, TN = 4;
 
-template <typename T>
-__global__ void __launch_bounds__(128)
+// Four values of a row from element i on (i a multiple of 4, the row 8- or 16-byte aligned).
+__device__ __forceinline__ void load4(float (&x)[4], const float* row, int i) {
+    const float4 v = *reinterpret_cast<const float4*>(row + i);
+    x[0] = v.x; x[1] = v.y; x[2] = v.z; x[3] = v.w;
+}
+__device__ __forceinline__ void load4(float (&x)[4], const bf16* row, int i) {
+    const uint2 v = *reinterpret_cast<const uint2*>(row + i);
+    x[0] = __uint_as_float(v.x << 16); x[1] = __uint_as_float(v.x & 0xffff0000u);
+    x[2] = __uint_as_float(v.y << 16); x[3] = __uint_as_float(v.y & 0xffff0000u);
+}
+
+// A block per TOK tokens.  Warp w forms the logits of experts w, w + warps, ...: a lane sums its
+// share of the row in rising order (four neighbouring elements at a time where the row's size and
+// place allow: `vec`), then the lanes are summed; a router row is read once for all TOK tokens.
+// The order of a token's sums depends on the sizes only, not on TOK or on the other tokens.
+// Then warp j chooses for token j.
+template <typename T, int TOK>
+__global__ void __launch_bounds__(512)
 moe_route_kernel(int* __restrict__ expert_of, float* __restrict__ weight_of, const T* __restrict__ h, long long ldh,
                  const float* __restrict__ router, const float* __restrict__ bias, int tokens, int hidden, int experts,
-                 int top) {
-    extern __shared__ float z_all[];                      // [warps][experts]
+                 int top, int vec) {
+    extern __shared__ float z_all[];                      // [TOK][experts]
     pdl_launch_dependents();
     pdl_wait();
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    const int t = blockIdx.x * (blockDim.x >> 5) + warp;
-    if (t >= tokens) return;
-    float* z = z_all + (size_t)warp * experts;
-    const T* row = h + (size_t)t * ldh;
-    for (int e = 0; e < experts; ++e) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+    const int t0 = blockIdx.x * TOK;
+    const T* rows[TOK];
+#pragma unroll
+    for (int j = 0; j < TOK; ++j) rows[j] = h + (size_t)min(t0 + j, tokens - 1) * ldh;
+    for (int e = warp; e < experts; e += warps) {
         const float* w = router + (size_t)e * hidden;
-        float acc = 0.f;
-        for (int i = lane; i < hidden; i += 32) acc = fmaf(w[i], to_f32(row[i]), acc);
-        acc = warp_sum(acc);
-        if (lane == 0) z[e] = acc + (bias ? bias[e] : 0.f);
-    }
-    __syncwarp();
-    for (int k = 0; k < top; ++k) {
-        float best = -INFINITY;
-        int idx = INT_MAX;
-        for (int e = lane; e < experts; e += 32) {
-            const float v = z[e];
-            if (v > best) { best = v; idx = e; }
+        float acc[TOK];
+#pragma unroll
+        for (int j = 0; j < TOK; ++j) acc[j] = 0.f;
+        if (vec) {
+#pragma unroll 4
+            for (int i = 4 * lane; i < hidden; i += 128) {
+                float wv[4];
+                load4(wv, w, i);
+#pragma unroll
+                for (int j = 0; j < TOK; ++j) {
+                    float x[4];
+                    load4(x, rows[j], i);
+#pragma unroll
+                    for (int u = 0; u < 4; ++u) acc[j] = fmaf(wv[u], x[u], acc[j]);
+                }
+            }
+        } else {
+#pragma unroll 4
+            for (int i = lane; i < hidden; i += 32) {
+                const float wv = w[i];
+#pragma unroll
+                for (int j = 0; j < TOK; ++j) acc[j] = fmaf(wv, to_f32(rows[j][i]), acc[j]);
+            }
         }
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) {
-            const float ov = __shfl_xor_sync(0xffffffffu, best, o);
-            const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
-            if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+        for (int j = 0; j < TOK; ++j) {
+            const float sum = warp_sum(acc[j]);
+            if (lane == 0) z_all[(size_t)j * experts + e] = sum + (bias ? bias[e] : 0.f);
         }
-        if (idx >= experts) { idx = k; best = 0.f; }      // logits that are no numbers: still a valid expert
-        if (lane == 0) {
-            expert_of[(size_t)t * top + k] = idx;
-            weight_of[(size_t)t * top + k] = best;
-            z[idx] = -INFINITY;
-        }
-        __syncwarp();
     }
-    if (lane == 0) {
-        float* w = weight_of + (size_t)t * top;
-        const float m = w[0];                            // the largest of the chosen
-        float sum = 0.f;
-        for (int k = 0; k < top; ++k) { w[k] = expf(w[k] - m); sum += w[k]; }
-        const float inv = 1.0f / sum;
-        for (int k = 0; k < top; ++k) w[k] *= inv;
+    __syncthreads();
+    for (int j = warp; j < TOK; j += warps) {
+        const int t = t0 + j;
+        if (t >= tokens) continue;
+        float* z = z_all + (size_t)j * experts;
+        for (int k = 0; k < top; ++k) {
+            float best = -INFINITY;
+            int idx = INT_MAX;
+            for (int e = lane; e < experts; e += 32) {
+                const float v = z[e];
+                if (v > best) { best = v; idx = e; }
+            }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) {
+                const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+                const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
+                if (ov > best || (ov == best && oi < idx)) { best = ov; idx = oi; }
+            }
+            if (idx >= experts) { idx = k; best = 0.f; }      // logits that are no numbers: still a valid expert
+            if (lane == 0) {
+                expert_of[(size_t)t * top + k] = idx;
+                weight_of[(size_t)t * top + k] = best;
+                z[idx] = -INFINITY;
+            }
+            __syncwarp();
+        }
+        if (lane == 0) {
+            float* w = weight_of + (size_t)t * top;
+            const float m = w[0];                            // the largest of the chosen
+            float sum = 0.f;
+            for (int k = 0; k < top; ++k) { w[k] = expf(w[k] - m); sum += w[k]; }
+            const float inv = 1.0f / sum;
+            for (int k = 0; k < top; ++k) w[k] *= inv;
+        }
     }
 }
 
@@ -103,6 +154,46 @@ moe_lists_kernel(int* __restrict__ sorted_pair, int* __restrict__ tile_info, int
     __syncthreads();
     // a pair's place among its expert's rows is whatever the race gives: its row's value does not depend on it
     for (int p = threadIdx.x; p < pairs; p += blockDim.x) sorted_pair[atomicAdd(&cursor[expert_of[p]], 1)] = p;
+}
+
+// The pairs sorted by expert with every expert's rows padded to whole tiles of `tile_rows`:
+// place_of_pair [pairs] (a pair's row among the padded rows), expert_of_tile [tiles], n_tiles [1].
+__global__ void __launch_bounds__(1024)
+moe_padded_lists_kernel(int* __restrict__ place_of_pair, int* __restrict__ expert_of_tile, int* __restrict__ n_tiles,
+                        const int* __restrict__ expert_of, int pairs, int experts, int tile_rows) {
+    extern __shared__ int lists[];                        // counts [experts], cursor [experts]
+    int* counts = lists;
+    int* cursor = lists + experts;
+    pdl_launch_dependents();
+    pdl_wait();
+    for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
+    __syncthreads();
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&counts[expert_of[p]], 1);
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int nt = 0;
+        for (int e = 0; e < experts; ++e) {
+            cursor[e] = nt * tile_rows;
+            for (int r0 = 0; r0 < counts[e]; r0 += tile_rows) expert_of_tile[nt++] = e;
+        }
+        *n_tiles = nt;
+    }
+    __syncthreads();
+    // a pair's place among its expert's rows is whatever the race gives: its row's value does not depend on it
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x) place_of_pair[p] = atomicAdd(&cursor[expert_of[p]], 1);
+}
+
+// dst[place_of_pair[p], :] = src[p / top, :], 16 bytes per thread and step (bfloat16 rows of 8 n elements).
+__global__ void __launch_bounds__(256)
+moe_gather_rows_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, long long ld_src16, int row16,
+                       const int* __restrict__ place_of_pair, int pairs, int top) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int p = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    if (p >= pairs) return;
+    const uint4* from = src + (size_t)(p / top) * ld_src16;
+    uint4* to = dst + (size_t)place_of_pair[p] * row16;
+    for (int i = threadIdx.x & 31; i < row16; i += 32) to[i] = from[i];
 }
 
 struct GemmArgs {
@@ -281,14 +372,17 @@ moe_gemm_mma_kernel(const GemmArgs g) {
 
 __global__ void __launch_bounds__(128)
 moe_combine_kernel(float* __restrict__ y, const float* __restrict__ rows, const float* __restrict__ weight_of, int hidden,
-                   int top) {
+                   int top, const int* __restrict__ place_of_pair) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
     const float* w = weight_of + (size_t)t * top;
     for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
         float acc = 0.f;
-        for (int k = 0; k < top; ++k) acc = fmaf(w[k], rows[((size_t)t * top + k) * hidden + i], acc);
+        for (int k = 0; k < top; ++k) {
+            const size_t row = place_of_pair ? (size_t)place_of_pair[(size_t)t * top + k] : (size_t)t * top + k;
+            acc = fmaf(w[k], rows[row * hidden + i], acc);
+        }
         y[(size_t)t * hidden + i] += acc;
     }
 }
@@ -302,15 +396,28 @@ extern "C" int kipp_moe_route(int* expert_of, float* weight_of, const void* h, l
                               const float* bias, int tokens, int hidden, int experts, int top, void* stream) {
     if (tokens <= 0) return 0;
     if (hidden <= 0 || experts <= 0 || top <= 0 || top > experts || experts > 2048) return KIPP_ERR_ARG;
-    const dim3 grid((unsigned)((tokens + 3) / 4));
-    const size_t smem = (size_t)4 * experts * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == KIPP_DT_F32)
-        return kipp_launch(moe_route_kernel<float>, grid, dim3(128), smem, s, 1, expert_of, weight_of, (const float*)h, ldh,
-                           router, bias, tokens, hidden, experts, top);
-    if (dtype == KIPP_DT_BF16)
-        return kipp_launch(moe_route_kernel<bf16>, grid, dim3(128), smem, s, 1, expert_of, weight_of, (const bf16*)h, ldh,
-                           router, bias, tokens, hidden, experts, top);
+    const size_t es = dtype == KIPP_DT_F32 ? 4 : 2;
+    const int vec = hidden % 4 == 0 && ldh % 4 == 0 && ((uintptr_t)h % (4 * es)) == 0 && ((uintptr_t)router & 15) == 0;
+    // many tokens: four per block share a read of the router; few: a warp per expert, up to sixteen
+    const int tok = tokens >= 256 ? 4 : 1;
+    const int warps = tok == 4 ? 8 : (experts >= 16 ? 16 : experts > 8 ? 8 : 4);
+    const dim3 grid((unsigned)((tokens + tok - 1) / tok)), block((unsigned)(32 * warps));
+    const size_t smem = (size_t)tok * experts * sizeof(float);
+    if (dtype == KIPP_DT_F32) {
+        if (tok == 4)
+            return kipp_launch(moe_route_kernel<float, 4>, grid, block, smem, s, 1, expert_of, weight_of, (const float*)h,
+                               ldh, router, bias, tokens, hidden, experts, top, vec);
+        return kipp_launch(moe_route_kernel<float, 1>, grid, block, smem, s, 1, expert_of, weight_of, (const float*)h, ldh,
+                           router, bias, tokens, hidden, experts, top, vec);
+    }
+    if (dtype == KIPP_DT_BF16) {
+        if (tok == 4)
+            return kipp_launch(moe_route_kernel<bf16, 4>, grid, block, smem, s, 1, expert_of, weight_of, (const bf16*)h, ldh,
+                               router, bias, tokens, hidden, experts, top, vec);
+        return kipp_launch(moe_route_kernel<bf16, 1>, grid, block, smem, s, 1, expert_of, weight_of, (const bf16*)h, ldh,
+                           router, bias, tokens, hidden, experts, top, vec);
+    }
     return KIPP_ERR_DTYPE;
 }
 
@@ -352,11 +459,35 @@ extern "C" int kipp_moe_gemm(void* out, int out_dtype, long long ldo, const void
     return KIPP_ERR_DTYPE;
 }
 
-// y[t, :] += sum_k weight_of[t, k] * rows[t * top + k, :], k in order.
+// y[t, :] += sum_k weight_of[t, k] * rows[r, :], k in order; r = t * top + k, or place_of_pair[t * top + k] if given.
 extern "C" int kipp_moe_combine(float* y, const float* rows, const float* weight_of, int tokens, int hidden, int top,
-                                void* stream) {
+                                const int* place_of_pair, void* stream) {
     if (tokens <= 0) return 0;
     if (hidden <= 0 || top <= 0) return KIPP_ERR_ARG;
     return kipp_launch(moe_combine_kernel, dim3((unsigned)tokens), dim3(128), 0, (cudaStream_t)stream, 1, y, rows, weight_of,
-                       hidden, top);
+                       hidden, top, place_of_pair);
+}
+
+// Tiles of `tile_rows` rows that `pairs` pairs over `experts` experts can need at most when every
+// expert's rows are padded to whole tiles.
+extern "C" int kipp_moe_max_padded_tiles(int pairs, int experts, int tile_rows) {
+    return pairs / tile_rows + (experts < pairs ? experts : pairs);
+}
+
+// place_of_pair [pairs], expert_of_tile [kipp_moe_max_padded_tiles], n_tiles [1]
+extern "C" int kipp_moe_padded_lists(int* place_of_pair, int* expert_of_tile, int* n_tiles, const int* expert_of, int pairs,
+                                     int experts, int tile_rows, void* stream) {
+    if (pairs <= 0) return 0;
+    if (experts <= 0 || experts > 2048 || tile_rows <= 0) return KIPP_ERR_ARG;
+    return kipp_launch(moe_padded_lists_kernel, dim3(1), dim3(1024), (size_t)2 * experts * sizeof(int), (cudaStream_t)stream,
+                       1, place_of_pair, expert_of_tile, n_tiles, expert_of, pairs, experts, tile_rows);
+}
+
+// dst[place_of_pair[p], 0 .. hidden) = src[p / top, 0 .. hidden), bfloat16, hidden and ld_src multiples of 8.
+extern "C" int kipp_moe_gather_rows(void* dst, const void* src, long long ld_src, const int* place_of_pair, int pairs,
+                                    int top, int hidden, void* stream) {
+    if (pairs <= 0) return 0;
+    if (hidden <= 0 || hidden % 8 || ld_src % 8 || top <= 0 || (((uintptr_t)dst | (uintptr_t)src) & 15)) return KIPP_ERR_ARG;
+    return kipp_launch(moe_gather_rows_kernel, dim3((unsigned)((pairs + 7) / 8)), dim3(256), 0, (cudaStream_t)stream, 1,
+                       (uint4*)dst, (const uint4*)src, ld_src / 8, hidden / 8, place_of_pair, pairs, top);
 }
