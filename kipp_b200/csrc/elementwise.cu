@@ -370,31 +370,65 @@ extern "C" int kipp_keep_last_token(int* last_token, long long stride, const int
 
 // ---------------------------------------------------------------------------
 // x[r, :] += mult * y[r, :] * rsqrt(mean(y[r, :]^2) + eps) * w: the RMS norm of a sublayer's OUTPUT
-// joins the residual stream, all of it float32 (w keeps its storage type).
+// joins the residual stream, all of it float32 (w keeps its storage type).  `copy` (or null) takes
+// the new x rounded to bfloat16: the input of the sublayer that reads the stream next.
 __global__ void __launch_bounds__(256)
 rmsnorm_scaled_add_kernel(float* __restrict__ x, const float* __restrict__ y, const void* __restrict__ w, int w_dtype,
-                          int size, float eps, float mult) {
+                          int size, float eps, float mult, bf16* __restrict__ copy, int vec) {
     __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
     const float* src = y + (size_t)blockIdx.x * size;
     float* dst = x + (size_t)blockIdx.x * size;
+    bf16* cp = copy ? copy + (size_t)blockIdx.x * size : nullptr;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < size; i += blockDim.x) ss = fmaf(src[i], src[i], ss);
+    if (vec) {
+        // four neighbouring values per thread and step; the order of a row's sum depends on its size only
+        for (int i = 4 * threadIdx.x; i < size; i += 4 * blockDim.x) {
+            const float4 v = *reinterpret_cast<const float4*>(src + i);
+            ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+        }
+    } else {
+        for (int i = threadIdx.x; i < size; i += blockDim.x) ss = fmaf(src[i], src[i], ss);
+    }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)size + eps);
-    for (int i = threadIdx.x; i < size; i += blockDim.x) {
-        const float wi = w_dtype == KIPP_DT_F32 ? static_cast<const float*>(w)[i] : to_f32(static_cast<const bf16*>(w)[i]);
-        dst[i] += mult * (src[i] * inv * wi);
+    auto weight = [&](int i) {
+        return w_dtype == KIPP_DT_F32 ? static_cast<const float*>(w)[i] : to_f32(static_cast<const bf16*>(w)[i]);
+    };
+    if (vec) {
+        for (int i = 4 * threadIdx.x; i < size; i += 4 * blockDim.x) {
+            const float4 v = *reinterpret_cast<const float4*>(src + i);
+            float4 o = *reinterpret_cast<const float4*>(dst + i);
+            o.x += mult * (v.x * inv * weight(i));
+            o.y += mult * (v.y * inv * weight(i + 1));
+            o.z += mult * (v.z * inv * weight(i + 2));
+            o.w += mult * (v.w * inv * weight(i + 3));
+            *reinterpret_cast<float4*>(dst + i) = o;
+            if (cp) {
+                const __nv_bfloat162 lo = __floats2bfloat162_rn(o.x, o.y), hi = __floats2bfloat162_rn(o.z, o.w);
+                uint2 pk;
+                pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+                pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+                *reinterpret_cast<uint2*>(cp + i) = pk;
+            }
+        }
+    } else {
+        for (int i = threadIdx.x; i < size; i += blockDim.x) {
+            const float o = dst[i] + mult * (src[i] * inv * weight(i));
+            dst[i] = o;
+            if (cp) cp[i] = __float2bfloat16_rn(o);
+        }
     }
 }
 
 extern "C" int kipp_rmsnorm_scaled_add(float* x, const float* y, const void* w, int w_dtype, int rows, int size, float eps,
-                                       float mult, void* stream) {
+                                       float mult, void* copy_bf16, void* stream) {
     if (rows <= 0) return 0;
     if (size <= 0 || !(eps > 0.f) || (w_dtype != KIPP_DT_F32 && w_dtype != KIPP_DT_BF16)) return KIPP_ERR_ARG;
+    const int vec = size % 4 == 0 && (((uintptr_t)x | (uintptr_t)y) & 15) == 0 && ((uintptr_t)copy_bf16 & 7) == 0;
     return kipp_launch(rmsnorm_scaled_add_kernel, dim3((unsigned)rows), dim3(size >= 1024 ? 256 : 128), 0, (cudaStream_t)stream,
-                       1, x, y, w, w_dtype, size, eps, mult);
+                       1, x, y, w, w_dtype, size, eps, mult, (bf16*)copy_bf16, vec);
 }
 
 // x *= scale over n float32 values (logits of a head with a scale).

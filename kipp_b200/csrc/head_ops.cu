@@ -94,10 +94,24 @@ head_segments_kernel(const SegmentArgs a, int* __restrict__ status) {
         // every warp of the token sums the whole run of heads in the same order
         const T* all = static_cast<const T*>(a.src) + (size_t)t * a.ld_src + g.src_off;
         const int n = g.heads * D;
+        constexpr int VEC = 16 / (int)sizeof(T);
         float ss = 0.f;
-        for (int i = lane; i < n; i += 32) {
-            const float v = to_f32(all[i]) + (g.bias ? g.bias[i] : 0.f);
-            ss = fmaf(v, v, ss);
+        if (g.bias == nullptr && n % VEC == 0 && ((uintptr_t)all & 15) == 0) {
+            // 16 bytes per lane and step (the same lanes take the same elements for every head's warp)
+            for (int i = VEC * lane; i < n; i += 32 * VEC) {
+                const uint4 raw = *reinterpret_cast<const uint4*>(all + i);
+                const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+                for (int j = 0; j < VEC; ++j) {
+                    const float v = to_f32(e[j]);
+                    ss = fmaf(v, v, ss);
+                }
+            }
+        } else {
+            for (int i = lane; i < n; i += 32) {
+                const float v = to_f32(all[i]) + (g.bias ? g.bias[i] : 0.f);
+                ss = fmaf(v, v, ss);
+            }
         }
         inv = 1.0f / sqrtf(warp_sum(ss) / (float)n + a.eps);
         norm_w = g.norm_w + (size_t)hh * D;

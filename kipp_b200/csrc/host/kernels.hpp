@@ -486,11 +486,12 @@ public:
         run(f(last_token, stride, ids, q_start, slots, entries, stream), "keep_last_token");
     }
     // x[r, :] += mult * y[r, :] * rsqrt(mean(y[r, :]^2) + eps) * w, all float32 (w keeps its storage type)
+    // copy_bf16 (or null): the new x rounded to bfloat16, for the sublayer that reads the stream next
     void rmsnorm_scaled_add(float* x, const float* y, const void* w, int w_dtype, int rows, int size, float eps,
-                            float mult) {
-        using Fn = int (*)(float*, const float*, const void*, int, int, int, float, float, void*);
+                            float mult, void* copy_bf16 = nullptr) {
+        using Fn = int (*)(float*, const float*, const void*, int, int, int, float, float, void*, void*);
         static Fn f = kernel_symbol<Fn>("elementwise", "kipp_rmsnorm_scaled_add");
-        run(f(x, y, w, w_dtype, rows, size, eps, mult, stream), "rmsnorm_scaled_add");
+        run(f(x, y, w, w_dtype, rows, size, eps, mult, copy_bf16, stream), "rmsnorm_scaled_add");
     }
     void scale_f32(float* x, long long n, float scale) {
         using Fn = int (*)(float*, long long, float, void*);
@@ -560,10 +561,10 @@ public:
                   int dtype, int N, int K, int top, bool gather, bool scatter, int activation, const int* sorted_pair,
                   const int* tile_info, const int* n_tiles, int pairs, int experts) {
         using Fn = int (*)(void*, int, long long, const void*, long long, const void*, long long, int, int, int, int, int,
-                           int, int, const int*, const int*, const int*, int, int, int, void*);
+                           int, int, const int*, const int*, const int*, int, int, void*);
         static Fn f = kernel_symbol<Fn>("moe", "kipp_moe_gemm");
         run(f(out, out_dtype, ldo, a, lda, w, w_expert, dtype, N, K, top, gather ? 1 : 0, scatter ? 1 : 0, activation,
-              sorted_pair, tile_info, n_tiles, pairs, experts, moe_tensor_core ? 1 : 0, stream),
+              sorted_pair, tile_info, n_tiles, pairs, experts, stream),
             "moe_gemm", 1, profiling ? format("moe_gemm %d x %d", N, K).c_str() : nullptr);
     }
     void moe_combine(float* y, const float* rows, const float* weight_of, int tokens, int hidden, int top,

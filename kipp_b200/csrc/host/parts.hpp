@@ -932,20 +932,25 @@ public:
         ctx.emit_for = nullptr;
         ctx.emitted = false;
         float* y = ctx.workspace->get<float>("sublayer_output", (size_t)T * W);
-        auto sublayer = [&](const Norm& norm, auto&& run_part) {
+        // 16-bit path: a sublayer reads the stream rounded to the compute type.  The first
+        // sublayer's copy is made here; the second one's leaves the kernel that adds the first
+        // one's output to the stream.
+        void* hc = ctx.dtype != F32 ? ctx.workspace->buffer("normed", (size_t)T * W * ctx.element()) : nullptr;
+        auto sublayer = [&](const Norm& norm, bool copied, bool copy_after, auto&& run_part) {
             const void* h = x;                    // 32-bit path: the sublayer reads the stream in place
-            if (ctx.dtype != F32) {
-                void* hc = ctx.workspace->buffer("normed", (size_t)T * W * ctx.element());
-                ctx.ops->convert_rows(hc, ctx.dtype, W, x, F32, W, T, W);
+            if (hc != nullptr) {
+                if (!copied) ctx.ops->convert_rows(hc, ctx.dtype, W, x, F32, W, T, W);
                 h = hc;
             }
             cuda_check(cudaMemsetAsync(y, 0, (size_t)T * W * sizeof(float), ctx.stream), "clearing a sublayer's output");
             run_part(h);
             const RmsNormSpec spec = *norm.rms_spec();
-            ctx.ops->rmsnorm_scaled_add(x, y, spec.weight, spec.weight_dtype, T, W, spec.eps, mult_);
+            ctx.ops->rmsnorm_scaled_add(x, y, spec.weight, spec.weight_dtype, T, W, spec.eps, mult_,
+                                        copy_after && ctx.dtype == BF16 ? hc : nullptr);
         };
-        sublayer(*n1_, [&](const void* h) { mixer_->forward(ctx, run, 0, h, y); });
-        if (ffn_) sublayer(*n2_, [&](const void* h) { ffn_->forward(ctx, h, y); });
+        const bool hand_on = ffn_ != nullptr && ctx.dtype == BF16;
+        sublayer(*n1_, false, hand_on, [&](const void* h) { mixer_->forward(ctx, run, 0, h, y); });
+        if (ffn_) sublayer(*n2_, hand_on, false, [&](const void* h) { ffn_->forward(ctx, h, y); });
         ctx.emitted = false;
     }
     Norm* mixer_norm() { return n1_.get(); }

@@ -1,6 +1,6 @@
 // A feed-forward made of many small experts of which every token uses a few.
 //
-//   route     z = W_r h + b in float32 (a warp per token); the `top` largest logits are chosen (the
+//   route     z = W_r h + b in float32 (a warp per expert); the `top` largest logits are chosen (the
 //             lower index on a tie) and their weights are the softmax over the chosen logits only;
 //   lists     the (token, choice) pairs sorted by expert, cut into tiles of 64 rows that belong to
 //             one expert each; everything on the device, so that a step's launches do not depend
@@ -10,15 +10,15 @@
 //             times the expert's down projection into one float32 row per pair;
 //   combine   y[t] += sum over the token's choices, in the order of their rank, of weight x row.
 //
-// Prompt-sized steps in bfloat16 take another road for the two products: the pairs' input rows are
-// copied into a buffer sorted by expert in which every expert's rows are padded to whole tiles of 128
-// (padded lists, gather), and both products run as ONE grouped product each on the tcgen05 prompt
-// kernel of gemm_tc.cu, whose token tiles then meet one expert's weights each.
+// In bfloat16 (sizes that are multiples of 8) the two products take another road: the pairs' input
+// rows are copied into a buffer sorted by expert in which every expert's rows are padded to whole
+// tiles (padded lists, gather), and each projection is ONE grouped product on the tcgen05 kernels
+// of gemm_tc.cu, whose token tiles then meet one expert's weights each: tiles of 128 rows on the
+// prompt kernel for prompt-sized steps, of 16 rows on the few-token kernel otherwise.  The
+// products of this file (CUDA cores) serve float32 and the other sizes.
 //
 // A pair's row is computed from its own token alone, in an order of sums that depends on the
-// sizes only: the result does not depend on which other tokens share its tile.  The products run
-// on the tensor cores (mma.sync m16n8k16, bfloat16 in, float32 sums) or, in 32-bit and for sizes
-// that are no multiple of 8, on the CUDA cores.
+// sizes only: the result does not depend on which other tokens share its tile.
 #include "common.cuh"
 #include <math.h>
 #include <limits.h>
@@ -268,108 +268,6 @@ moe_gemm_kernel(const GemmArgs g) {
     }
 }
 
-__device__ __forceinline__ void mma_16816(float* c, const uint32_t* a, uint32_t b0, uint32_t b1) {
-    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
-                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
-}
-__device__ __forceinline__ void cp16(void* dst, const void* src, bool ok) {
-    const uint32_t d = (uint32_t)__cvta_generic_to_shared(dst);
-    const int n = ok ? 16 : 0;
-    asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(d), "l"(src), "r"(n));
-}
-
-// Tensor cores: a block of 4 warps per 64 rows x 128 features; K in steps of 32 through two shared
-// buffers filled by asynchronous copies.  Warp w owns features [32 w, 32 w + 32) of all 64 rows.
-constexpr int TBN = 128, TBK = 32, TLD = TBK + 8;
-template <typename TO>
-__global__ void __launch_bounds__(128)
-moe_gemm_mma_kernel(const GemmArgs g) {
-    __shared__ __align__(16) bf16 As[2][BM][TLD];
-    __shared__ __align__(16) bf16 Ws[2][TBN][TLD];
-    __shared__ int arow[BM], orow[BM];
-    pdl_launch_dependents();
-    pdl_wait();
-    const int tile = blockIdx.y;
-    if (tile >= *g.n_tiles) return;
-    const int e = g.tile_info[3 * tile], r0 = g.tile_info[3 * tile + 1], rows = g.tile_info[3 * tile + 2];
-    const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, gid = lane >> 2, tig = lane & 3;
-    if (tid < BM) {
-        const int pair = tid < rows ? g.sorted_pair[r0 + tid] : -1;
-        arow[tid] = pair < 0 ? -1 : (g.gather ? pair / g.top : r0 + tid);
-        orow[tid] = pair < 0 ? -1 : (g.scatter ? pair : r0 + tid);
-    }
-    __syncthreads();
-    const bf16* A = static_cast<const bf16*>(g.a);
-    const bf16* W = static_cast<const bf16*>(g.w) + (size_t)e * g.w_expert;
-    const int n0 = blockIdx.x * TBN, N = g.N, K = g.K;
-    auto load = [&](int buf, int k0) {
-        // 64 rows x 4 chunks of A, 128 rows x 4 chunks of W: 16-byte chunks of 8 elements
-        for (int i = tid; i < BM * 4; i += 128) {
-            const int r = i >> 2, c = (i & 3) * 8;
-            const bool ok = arow[r] >= 0 && k0 + c < K;
-            cp16(&As[buf][r][c], ok ? A + (size_t)arow[r] * g.lda + k0 + c : A, ok);
-        }
-        for (int i = tid; i < TBN * 4; i += 128) {
-            const int r = i >> 2, c = (i & 3) * 8;
-            const bool ok = n0 + r < N && k0 + c < K;
-            cp16(&Ws[buf][r][c], ok ? W + (size_t)(n0 + r) * K + k0 + c : W, ok);
-        }
-        asm volatile("cp.async.commit_group;");
-    };
-    float acc[4][4][4];
-#pragma unroll
-    for (int m = 0; m < 4; ++m)
-#pragma unroll
-        for (int n = 0; n < 4; ++n) acc[m][n][0] = acc[m][n][1] = acc[m][n][2] = acc[m][n][3] = 0.f;
-    load(0, 0);
-    int buf = 0;
-    for (int k0 = 0; k0 < K; k0 += TBK, buf ^= 1) {
-        if (k0 + TBK < K) load(buf ^ 1, k0 + TBK);
-        else asm volatile("cp.async.commit_group;");
-        asm volatile("cp.async.wait_group 1;");
-        __syncthreads();
-#pragma unroll
-        for (int ks = 0; ks < TBK; ks += 16) {
-            uint32_t b[4][2];
-#pragma unroll
-            for (int n = 0; n < 4; ++n) {
-                const bf16* wr = &Ws[buf][warp * 32 + n * 8 + gid][ks + tig * 2];
-                b[n][0] = *reinterpret_cast<const uint32_t*>(wr);
-                b[n][1] = *reinterpret_cast<const uint32_t*>(wr + 8);
-            }
-#pragma unroll
-            for (int m = 0; m < 4; ++m) {
-                uint32_t a[4];
-                const bf16* ar = &As[buf][m * 16 + gid][ks + tig * 2];
-                a[0] = *reinterpret_cast<const uint32_t*>(ar);
-                a[1] = *reinterpret_cast<const uint32_t*>(ar + 8 * TLD);
-                a[2] = *reinterpret_cast<const uint32_t*>(ar + 8);
-                a[3] = *reinterpret_cast<const uint32_t*>(ar + 8 * TLD + 8);
-#pragma unroll
-                for (int n = 0; n < 4; ++n) mma_16816(acc[m][n], a, b[n][0], b[n][1]);
-            }
-        }
-        __syncthreads();
-    }
-    TO* out = static_cast<TO*>(g.out);
-#pragma unroll
-    for (int m = 0; m < 4; ++m)
-#pragma unroll
-        for (int half = 0; half < 2; ++half) {
-            const int orw = orow[m * 16 + gid + half * 8];
-            if (orw < 0) continue;
-#pragma unroll
-            for (int n = 0; n < 4; ++n)
-#pragma unroll
-                for (int j = 0; j < 2; ++j) {
-                    const int col = n0 + warp * 32 + n * 8 + tig * 2 + j;
-                    const float v = acc[m][n][half * 2 + j];
-                    if (col < N) out[(size_t)orw * g.ldo + col] = from_f32<TO>(g.act >= 0 ? kipp_activation(v, g.act) : v);
-                }
-        }
-}
-
 __global__ void __launch_bounds__(128)
 moe_combine_kernel(float* __restrict__ y, const float* __restrict__ rows, const float* __restrict__ weight_of, int hidden,
                    int top, const int* __restrict__ place_of_pair) {
@@ -432,11 +330,12 @@ extern "C" int kipp_moe_lists(int* sorted_pair, int* tile_info, int* n_tiles, co
 
 // One product of every tile: out rows = act(A rows x W[expert]^T).  gather: a row of A is the pair's
 // token (else its place in the sorted list); scatter: a row of out is the pair (else its place in the
-// sorted list).  A and W in `dtype`; out in `out_dtype`.  tensor_core 0 keeps the CUDA-core kernel.
+// sorted list).  A and W in `dtype`; out in `out_dtype`.  On the CUDA cores: float32, and sizes the
+// grouped tensor-core products cannot take.
 extern "C" int kipp_moe_gemm(void* out, int out_dtype, long long ldo, const void* a, long long lda, const void* w,
                              long long w_expert, int dtype, int N, int K, int top, int gather, int scatter, int act,
                              const int* sorted_pair, const int* tile_info, const int* n_tiles, int pairs, int experts,
-                             int tensor_core, void* stream) {
+                             void* stream) {
     if (pairs <= 0) return 0;
     if (N <= 0 || K <= 0 || top <= 0 || experts <= 0) return KIPP_ERR_ARG;
     GemmArgs g;
@@ -445,13 +344,6 @@ extern "C" int kipp_moe_gemm(void* out, int out_dtype, long long ldo, const void
     g.sorted_pair = sorted_pair; g.tile_info = tile_info; g.n_tiles = n_tiles;
     const int tiles = kipp_moe_max_tiles(pairs, experts);
     cudaStream_t s = (cudaStream_t)stream;
-    const bool aligned = K % 8 == 0 && lda % 8 == 0 && w_expert % 8 == 0 && (((uintptr_t)a | (uintptr_t)w) & 15) == 0;
-    if (dtype == KIPP_DT_BF16 && tensor_core && aligned) {
-        const dim3 grid((unsigned)((N + TBN - 1) / TBN), (unsigned)tiles);
-        if (out_dtype == KIPP_DT_BF16) return kipp_launch(moe_gemm_mma_kernel<bf16>, grid, dim3(128), 0, s, 1, g);
-        if (out_dtype == KIPP_DT_F32) return kipp_launch(moe_gemm_mma_kernel<float>, grid, dim3(128), 0, s, 1, g);
-        return KIPP_ERR_DTYPE;
-    }
     const dim3 grid((unsigned)((N + BN - 1) / BN), (unsigned)tiles);
     if (dtype == KIPP_DT_F32 && out_dtype == KIPP_DT_F32) return kipp_launch(moe_gemm_kernel<float, float>, grid, dim3(256), 0, s, 1, g);
     if (dtype == KIPP_DT_BF16 && out_dtype == KIPP_DT_BF16) return kipp_launch(moe_gemm_kernel<bf16, bf16>, grid, dim3(256), 0, s, 1, g);
