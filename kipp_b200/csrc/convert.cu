@@ -58,6 +58,23 @@ __global__ void convert_rows_kernel(void* __restrict__ dst, int dst_dtype, long 
         }
     }
 }
+
+// float32 -> bfloat16, four values per thread and step (rows of 4 n values on 16-byte boundaries):
+// the rounding of the residual stream for a 16-bit sublayer is on the step's path.
+__global__ void __launch_bounds__(256)
+round_rows_kernel(bf16* __restrict__ dst, long long dst_pitch, const float* __restrict__ src, long long src_pitch,
+                  long long rows, long long quads) {
+    const long long n = rows * quads;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < n; i += (long long)gridDim.x * blockDim.x) {
+        const long long r = i / quads, c = 4 * (i - r * quads);
+        const float4 v = *reinterpret_cast<const float4*>(src + r * src_pitch + c);
+        const __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        uint2 pk;
+        pk.x = *reinterpret_cast<const uint32_t*>(&lo);
+        pk.y = *reinterpret_cast<const uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(dst + r * dst_pitch + c) = pk;
+    }
+}
 }  // namespace
 
 // dst[r * dst_pitch + c] = convert(src[r * src_pitch + c]); pitches in elements.
@@ -68,6 +85,14 @@ extern "C" int kipp_convert_rows(void* dst, int dst_dtype, long long dst_pitch, 
     const bool float_src = src_dtype == KIPP_DT_F32 || src_dtype == KIPP_DT_BF16 || src_dtype == KIPP_DT_F16;
     const bool int_src = src_dtype >= KIPP_DT_I32 && src_dtype <= KIPP_DT_U8;
     if (!(float_dst && float_src) && !(dst_dtype == KIPP_DT_I32 && int_src)) return KIPP_ERR_DTYPE;
+    if (dst_dtype == KIPP_DT_BF16 && src_dtype == KIPP_DT_F32 && cols % 4 == 0 && dst_pitch % 4 == 0 && src_pitch % 4 == 0 &&
+        ((uintptr_t)dst & 7) == 0 && ((uintptr_t)src & 15) == 0) {
+        long long blocks = (rows * (cols / 4) + 255) / 256;
+        if (blocks > 148 * 16) blocks = 148 * 16;
+        round_rows_kernel<<<(unsigned)blocks, 256, 0, (cudaStream_t)stream>>>((bf16*)dst, dst_pitch, (const float*)src,
+                                                                             src_pitch, rows, cols / 4);
+        return kipp_launch_status();
+    }
     const long long n = rows * cols;
     long long blocks = (n + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;

@@ -103,7 +103,7 @@ def test_presets_are_data_and_valid():
     preset has the sizes of the 4B benchmark configuration."""
     from kipp_b200.config import config_from_dict, load_preset, preset_names
     names = preset_names()
-    assert {"tiny-a", "tiny-b", "venizen-tiny", "varunex-tiny", "qwen3-4b", "qwen3-8b", "qwen3-32b"} <= set(names)
+    assert {"tiny-a", "tiny-b", "venizen-tiny", "varunex-tiny", "zasudra-tiny", "qwen3-4b", "qwen3-8b", "qwen3-32b"} <= set(names)
     for name in names:
         cfg_dict, init = load_preset(name)
         cfg = config_from_dict(cfg_dict)                     # the architecture's own checks run here

@@ -441,6 +441,32 @@ def test_greedy_generation_through_the_scheduler(name):
         assert result.tokens == seq[len(prompt):]
 
 
+def test_the_command_line_generates_greedily_and_samples():
+    name = "D"
+    vocab = CONFIGS[name]["vocab"]
+    a, b = random_tokens(vocab, 9, seed=5), random_tokens(vocab, 27, seed=6)
+    proc = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "kipp"), "--model", model_folder(name),
+                           "--prompt-ids", ",".join(map(str, a)), "--prompt-ids", ",".join(map(str, b)),
+                           "--decode", "5", "--dtype", "float32", "--chunk", "16", "--top", "0"],
+                          capture_output=True, text=True, timeout=600)
+    assert proc.returncode == 0, proc.stderr[-2000:]
+    got = [[int(t) for t in line.split("\t")[1].split()] for line in proc.stdout.strip().splitlines()]
+    w = weights_for(name, "float32")
+    for prompt, tokens in zip((a, b), got):
+        seq = list(prompt)
+        with torch.no_grad():
+            for _ in range(5):
+                seq.append(int(P.forward(CONFIGS[name], w, seq)[-1].argmax()))
+        assert tokens == seq[len(prompt):]
+    assert "prefill_tokens=36" in proc.stderr and "decode_tokens=10" in proc.stderr
+    sampled = subprocess.run([sys.executable, os.path.join(ROOT, "bin", "kipp"), "--random", "zasudra-tiny",
+                              "--prompt-ids", "1,2,3,4,5", "--decode", "8", "--temperature", "0.8", "--top-k", "20",
+                              "--seed", "3", "--top", "0"], capture_output=True, text=True, timeout=600)
+    assert sampled.returncode == 0, sampled.stderr[-2000:]
+    tokens = [int(t) for t in sampled.stdout.strip().splitlines()[0].split("\t")[1].split()]
+    assert len(tokens) == 8 and all(0 <= t < 384 for t in tokens)
+
+
 def test_the_trace_program_runs_the_model_step_by_step(tmp_path):
     import numpy as np
     name = "B"
