@@ -338,6 +338,16 @@ def test_keys_just_inside_and_outside_a_block(block, dtype, tmp_path):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_many_narrow_heads(dtype, tmp_path):
+    """36 heads in all (28 query, 4 key, 4 value) of 8 dims, seven query heads on a key head: the
+    whole-projection norm over many heads; both kinds of layer."""
+    cfg = {"architecture": "Zasudra", "vocab": 97, "width": 56, "norm": {"eps": 1e-5}, "residual_mult": 0.8,
+           "layers": [blocks_layer(28, 4, 8, 24, 6, None, scale=0.6), gated_layer(28, 4, 8, 16, None, scale=0.5)]}
+    folder = write_folder(str(tmp_path / "m"), cfg, dict(seed=19, sigma=0.25, norm_jitter=0.2))
+    _needle_run(cfg, folder, dtype, random_tokens(97, 80, seed=9), [0, 1, 23, 24, 25, 79])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_a_far_key_among_hundreds_and_a_borrowed_cache(dtype, tmp_path):
     """Causal attention over 400 keys, sharp; the second layer reads the first one's keys
     and values with queries and a scale of its own."""
