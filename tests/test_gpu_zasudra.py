@@ -435,6 +435,93 @@ def test_long_decoding_of_a_batch_through_graphs(dtype):
     close(torch.cat(got_b), (plain_logits(name, dtype, b)[5:], None), dtype, "b")
 
 
+def _drawn_config(seed):
+    """A configuration drawn from a seed: layer order, head counts, head sizes (odd ones too), value
+    sizes, blocks, rotated dims, experts and choices, borrowed caches, optional keys left out."""
+    import random
+    r = random.Random(seed)
+    width = r.choice([40, 52, 64, 72, 96])
+    cfg = {"architecture": "Zasudra", "vocab": r.choice([89, 130, 257]), "width": width, "norm": {"eps": r.choice([1e-6, 1e-5, 3e-5])}}
+    if r.random() < 0.7:
+        cfg["residual_mult"] = r.choice([0.4, 0.9, 1.7])
+    if r.random() < 0.7:
+        cfg["logit_scale"] = r.choice([0.3, 2.0])
+    if r.random() < 0.7:
+        cfg["embedding"] = {"bigram": {"buckets": r.choice([1, 13, 211]), "mul_prev": r.choice([1, 29, 1000003]), "mul_cur": r.choice([1, 5, 40009])}}
+
+    def mlp():
+        if r.random() < 0.25:
+            return None
+        experts = r.choice([1, 2, 3, 7, 10])
+        return moe(experts, r.randint(1, experts), r.choice([6, 16, 24, 40]))
+    layers, lenders = [], []
+    for i in range(r.randint(3, 6)):
+        kind = r.choice(["attention", "attention_2", "wkv"])
+        if kind == "wkv":
+            layers.append(wkv_layer(r.choice([1, 2, 3]), r.choice([4, 6, 8, 16, 32]), r.choice([2, 5, 8]), mlp()))
+            continue
+        if kind == "attention_2" and lenders and r.random() < 0.5:
+            j = r.choice(lenders)
+            m = layers[j]["mixer"]
+            layers.append(gated_layer(m["heads"], m["kv_heads"], m["dim"], m["vdim"], mlp(), scale=r.choice([0.2, 0.5]), kv_from=j))
+            continue
+        kv = r.choice([1, 2, 3])
+        heads = kv * r.choice([1, 2, 4])
+        dim = r.choice([4, 6, 8, 10, 16, 32, 64])
+        scale = r.choice([0.5, 1.0, 2.0]) * dim ** -0.5
+        if kind == "attention":
+            rot = r.choice([0, 2, dim // 2 // 2 * 2, dim])
+            layers.append(blocks_layer(heads, kv, dim, r.choice([0, 1, 3, 16, 21, 50]), rot, mlp(), base=r.choice([100.0, 1e4, 5e5]), scale=scale))
+        else:
+            layers.append(gated_layer(heads, kv, dim, r.choice([dim, 4, 12, 24]), mlp(), scale=scale))
+            lenders.append(i)
+    cfg["layers"] = layers
+    return cfg
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_drawn_configurations(seed, tmp_path):
+    """Ten configurations nobody chose: 32-bit against the plain model (whole, in portions, and two
+    requests in one batch through one cache), bfloat16 whole against the plain model row by row."""
+    from kipp_b200.engine import Engine, StepEntry
+    cfg = _drawn_config(1000 + seed)
+    folder = write_folder(str(tmp_path / "m"), cfg, dict(seed=seed, sigma=0.15, norm_jitter=0.15))
+    a, b = random_tokens(cfg["vocab"], 75, seed=seed), random_tokens(cfg["vocab"], 40, seed=100 + seed)
+    for dtype in ("float32", "bfloat16"):
+        w = rounded(read_weights(folder), dtype)
+        with torch.no_grad():
+            want_a, want_b = P.forward(cfg, w, a), P.forward(cfg, w, b)
+        eng = Engine.from_folder(folder, dtype=dtype, page_size=16, cache_tokens=192, max_requests=2, max_batch_tokens=128)
+        whole = eng.step([StepEntry("w", a, list(range(len(a))))], check=True).clone()
+        eng.finish("w")
+        close(whole, (want_a, None), dtype, f"{cfg['layers']} whole")
+        if dtype == "bfloat16":
+            continue
+        got_a, got_b, at_a, at_b, i = [], [], 0, 0, 0
+        sizes_a, sizes_b = [2, 21, 1, 9, 30, 5, 7], [3, 1, 1, 17, 2, 16]
+        while at_a < len(a) or at_b < len(b):
+            entries = []
+            if at_a < len(a):
+                k = min(sizes_a[i % len(sizes_a)], len(a) - at_a)
+                entries.append(StepEntry("a", a[at_a:at_a + k], list(range(k))))
+            if at_b < len(b):
+                k = min(sizes_b[i % len(sizes_b)], len(b) - at_b)
+                entries.append(StepEntry("b", b[at_b:at_b + k], list(range(k))))
+            lg, row = eng.step(entries, check=True), 0
+            for e in entries:
+                k = len(e.tokens)
+                (got_a if e.request == "a" else got_b).append(lg[row:row + k].clone())
+                row += k
+                if e.request == "a":
+                    at_a += k
+                else:
+                    at_b += k
+            i += 1
+        close(torch.cat(got_a), want_a, dtype, "a in portions beside b")
+        close(torch.cat(got_b), want_b, dtype, "b in portions beside a")
+        assert nmse(torch.cat(got_a).cpu(), whole.cpu()) <= 1e-10
+
+
 @pytest.mark.parametrize("name", ["A", "C"])
 def test_greedy_generation_through_the_scheduler(name):
     from kipp_b200.engine.llm import LLM
