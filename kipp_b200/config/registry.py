@@ -72,4 +72,4 @@ def _ensure_builtin() -> None:
     if _builtin_done:
         return
     _builtin_done = True
-    from ..models import qwen3, varunex, venizen, zasudra  # noqa: F401  (they register themselves on import)
+    from ..models import qwen3, varunex, venizen, zasudra, zunilorn  # noqa: F401  (they register themselves on import)

@@ -103,9 +103,12 @@ struct MixExtras {
     long long ld_gate;
     int gate_off;
     int chunk;                 // > 0: blocks of this many positions bound what a query sees (no window then)
+    float softcap;             // > 0: a scaled score s becomes softcap * tanh(s / softcap) (before mix, mask and softmax)
 };
 
 __device__ __forceinline__ float sigmoid_(float x) { return 1.0f / (1.0f + expf(-x)); }
+// the scaled score, capped where the mixer asks for it
+__device__ __forceinline__ float capped(float s, float cap) { return cap > 0.f ? cap * tanhf(s / cap) : s; }
 
 // The factor that turns a head's unnormalised sum (maximum m, sum of weights l) into its output:
 // with a sink the denominator also holds e^sink.
@@ -263,8 +266,8 @@ attention_mix_kernel(T* __restrict__ out, const T* __restrict__ q, const T* __re
             __syncthreads();
             for (int idx = tid; idx < ng * group * KT; idx += THREADS) {
                 const int hl = idx / KT, jj = idx % KT, h = g0 * group + hl;
-                sraw[h * KT + jj] = dot_row(qs + h * head_dim, ktile + ((size_t)(hl / group) * KT + jj) * ldk + (h % maps) * head_dim,
-                                            head_dim, kdot) * scale;
+                sraw[h * KT + jj] = capped(dot_row(qs + h * head_dim, ktile + ((size_t)(hl / group) * KT + jj) * ldk + (h % maps) * head_dim,
+                                            head_dim, kdot) * scale, ex.softcap);
             }
         }
         __syncthreads();
@@ -606,10 +609,10 @@ attention_mix_mma_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, con
 #pragma unroll
             for (int mb = 0; mb < 2; ++mb) {
                 const int key = mb * 16 + gid;
-                sh[(tig * 2) * lds + key] = c[mb][0] * scale;
-                sh[(tig * 2 + 1) * lds + key] = c[mb][1] * scale;
-                sh[(tig * 2) * lds + key + 8] = c[mb][2] * scale;
-                sh[(tig * 2 + 1) * lds + key + 8] = c[mb][3] * scale;
+                sh[(tig * 2) * lds + key] = capped(c[mb][0] * scale, ex.softcap);
+                sh[(tig * 2 + 1) * lds + key] = capped(c[mb][1] * scale, ex.softcap);
+                sh[(tig * 2) * lds + key + 8] = capped(c[mb][2] * scale, ex.softcap);
+                sh[(tig * 2 + 1) * lds + key + 8] = capped(c[mb][3] * scale, ex.softcap);
             }
         }
         __syncthreads();                                            // all scores are there; K is no longer needed
@@ -941,10 +944,10 @@ attention_shared_key_kernel(bf16* __restrict__ out, const bf16* __restrict__ q, 
                 mma_16816(c, a, *reinterpret_cast<const uint32_t*>(kr + k0), *reinterpret_cast<const uint32_t*>(kr + k0 + 8));
             }
             const int key = warp * 8 + tig * 2;
-            sraw[gid * lds + key] = c[0] * scale;
-            sraw[gid * lds + key + 1] = c[1] * scale;
-            sraw[(gid + 8) * lds + key] = c[2] * scale;
-            sraw[(gid + 8) * lds + key + 1] = c[3] * scale;
+            sraw[gid * lds + key] = capped(c[0] * scale, ex.softcap);
+            sraw[gid * lds + key + 1] = capped(c[1] * scale, ex.softcap);
+            sraw[(gid + 8) * lds + key] = capped(c[2] * scale, ex.softcap);
+            sraw[(gid + 8) * lds + key + 1] = capped(c[3] * scale, ex.softcap);
         }
         __syncthreads();
         // ---- a softmax step for four head rows per warp (lane = key)

@@ -445,3 +445,209 @@ extern "C" int kipp_scale_f32(float* x, long long n, float scale, void* stream) 
     if (blocks > 0x7fffffffLL) return KIPP_ERR_ARG;
     return kipp_launch(scale_f32_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, 1, x, n, scale);
 }
+
+// ---------------------------------------------------------------------------------------------
+// Hyper-connections: the residual stream as S copies x_1 .. x_S, each [tokens, size] float32, `stride`
+// floats apart.  One launch does, per token row, up to two things in float32:
+//   update (y given)    x_t <- sum_s mix[s * S + t] x_s + mult * out[t] * y      for every t, from the old x_s
+//   read (in_w given)   u = sum_s in_w[s] x_s;  h = u * rsqrt(mean(u^2) + eps) * norm_w, in the compute type
+// so that the kernel between two sublayers writes the streams once and hands the next sublayer its
+// input.  With S = 1 and mix = in = out = 1 this is the plain residual add and pre-norm.
+namespace {
+constexpr int MAX_STREAMS = 8;
+struct HyperArgs {
+    float* x; long long stride; int S;
+    const float* y;
+    const float* mix; const float* out_w; float mult;
+    const float* in_w; const void* norm_w; int norm_w_dtype; float eps;
+    void* h;
+    int size;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+hyper_connection_kernel(const HyperArgs a) {
+    extern __shared__ float u_row[];                      // [size] when the read phase runs
+    __shared__ float scratch[32];
+    __shared__ float c_mix[MAX_STREAMS * MAX_STREAMS], c_out[MAX_STREAMS], c_in[MAX_STREAMS];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int S = a.S, size = a.size;
+    if (threadIdx.x < S * S && a.y != nullptr) c_mix[threadIdx.x] = a.mix ? a.mix[threadIdx.x] : (threadIdx.x % (S + 1) == 0 ? 1.f : 0.f);
+    if (threadIdx.x < S) {
+        c_out[threadIdx.x] = a.y != nullptr ? a.mult * (a.out_w ? a.out_w[threadIdx.x] : 1.f) : 0.f;
+        c_in[threadIdx.x] = a.in_w ? a.in_w[threadIdx.x] : 1.f;
+    }
+    __syncthreads();
+    const bool read = a.h != nullptr;
+    float* row = a.x + (size_t)blockIdx.x * size;
+    const float* yr = a.y ? a.y + (size_t)blockIdx.x * size : nullptr;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        float xs[MAX_STREAMS];
+#pragma unroll
+        for (int s = 0; s < MAX_STREAMS; ++s)
+            if (s < S) xs[s] = row[(size_t)s * a.stride + i];
+        if (yr != nullptr) {
+            const float y = yr[i];
+            float nx[MAX_STREAMS];
+#pragma unroll
+            for (int t = 0; t < MAX_STREAMS; ++t) {
+                if (t >= S) continue;
+                float acc = 0.f;
+#pragma unroll
+                for (int s = 0; s < MAX_STREAMS; ++s)
+                    if (s < S) acc = fmaf(c_mix[s * S + t], xs[s], acc);
+                nx[t] = fmaf(c_out[t], y, acc);
+            }
+#pragma unroll
+            for (int t = 0; t < MAX_STREAMS; ++t)
+                if (t < S) { xs[t] = nx[t]; row[(size_t)t * a.stride + i] = nx[t]; }
+        }
+        if (read) {
+            float u = 0.f;
+#pragma unroll
+            for (int s = 0; s < MAX_STREAMS; ++s)
+                if (s < S) u = fmaf(c_in[s], xs[s], u);
+            u_row[i] = u;
+            ss = fmaf(u, u, ss);
+        }
+    }
+    if (!read) return;
+    ss = block_sum(ss, scratch);
+    const float inv = 1.0f / sqrtf(ss / (float)size + a.eps);
+    T* h = static_cast<T*>(a.h) + (size_t)blockIdx.x * size;
+    for (int i = threadIdx.x; i < size; i += blockDim.x) {
+        const float w = a.norm_w_dtype == KIPP_DT_F32 ? static_cast<const float*>(a.norm_w)[i]
+                                                      : to_f32(static_cast<const bf16*>(a.norm_w)[i]);
+        h[i] = from_f32<T>(u_row[i] * inv * w);
+    }
+}
+
+__global__ void sum_streams_kernel(float* __restrict__ out, const float* __restrict__ x, long long stride, int S,
+                                   long long n) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float acc = 0.f;
+    for (int s = 0; s < S; ++s) acc += x[(size_t)s * stride + i];
+    out[i] = acc;
+}
+}  // namespace
+
+extern "C" int kipp_hyper_connection_max_streams() { return MAX_STREAMS; }
+
+// y null: no update; h null: no read.  mix [S, S] indexed [from, to], out_w [S], in_w [S] float32 (null: identity / ones).
+extern "C" int kipp_hyper_connection(float* x, long long stride, int streams, const float* y, const float* mix,
+                                     const float* out_w, float mult, const float* in_w, const void* norm_w,
+                                     int norm_w_dtype, float eps, void* h, int h_dtype, int rows, int size, void* stream) {
+    if (rows <= 0) return 0;
+    if (size <= 0 || streams <= 0 || streams > MAX_STREAMS || x == nullptr) return KIPP_ERR_ARG;
+    if (h != nullptr && (norm_w == nullptr || !(eps > 0.f) || (norm_w_dtype != KIPP_DT_F32 && norm_w_dtype != KIPP_DT_BF16)))
+        return KIPP_ERR_ARG;
+    if ((size_t)size * sizeof(float) > 160 * 1024) return KIPP_ERR_ARG;
+    HyperArgs a;
+    a.x = x; a.stride = stride; a.S = streams; a.y = y; a.mix = mix; a.out_w = out_w; a.mult = mult;
+    a.in_w = in_w; a.norm_w = norm_w; a.norm_w_dtype = norm_w_dtype; a.eps = eps; a.h = h; a.size = size;
+    const size_t smem = h != nullptr ? (size_t)size * sizeof(float) : 0;
+    const dim3 grid((unsigned)rows), block(size >= 1024 ? 256 : 128);
+    if (h == nullptr || h_dtype == KIPP_DT_F32) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(hyper_connection_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return kipp_launch(hyper_connection_kernel<float>, grid, block, smem, (cudaStream_t)stream, 1, a);
+    }
+    if (h_dtype == KIPP_DT_BF16) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(hyper_connection_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return kipp_launch(hyper_connection_kernel<bf16>, grid, block, smem, (cudaStream_t)stream, 1, a);
+    }
+    return KIPP_ERR_DTYPE;
+}
+
+// out[i] = sum_s x[s * stride + i] over n float32 values.
+extern "C" int kipp_sum_streams(float* out, const float* x, long long stride, int streams, long long n, void* stream) {
+    if (n <= 0) return 0;
+    if (streams <= 0) return KIPP_ERR_ARG;
+    const long long blocks = (n + 255) / 256;
+    if (blocks > 0x7fffffffLL) return KIPP_ERR_ARG;
+    return kipp_launch(sum_streams_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, 1, out, x, stride,
+                       streams, n);
+}
+
+// ---------------------------------------------------------------------------------------------
+// A gated feed-forward's activation with limits: g = min(gate + bg, limit), u = clamp(up + bu, -limit, limit),
+// out = g * sigmoid(alpha * g) * (u + 1), in float32 from the projection's stored values.  gate of element i
+// is proj[r, gate_off + i * step], up proj[r, up_off + i * step].  limit <= 0: no limits.  row_gate_col >= 0:
+// the whole row is also multiplied by sigmoid(proj[r, row_gate_col]) (a gate per token on the part's output:
+// applied here, before the linear down projection).
+namespace {
+template <typename T>
+__global__ void glu_limited_kernel(T* __restrict__ out, long long ld_out, const T* __restrict__ proj, long long ld_proj,
+                                   int rows, int n, int gate_off, int up_off, int step, const float* __restrict__ bias_gate,
+                                   const float* __restrict__ bias_up, float limit, float alpha, int row_gate_col) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)rows * n) return;
+    const long long r = idx / n;
+    const int i = (int)(idx % n);
+    const T* pr = proj + r * ld_proj;
+    float g = to_f32(pr[gate_off + (long long)i * step]), u = to_f32(pr[up_off + (long long)i * step]);
+    if (bias_gate != nullptr) g += bias_gate[i];
+    if (bias_up != nullptr) u += bias_up[i];
+    if (limit > 0.f) {
+        g = fminf(g, limit);
+        u = fminf(fmaxf(u, -limit), limit);
+    }
+    float v = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
+    if (row_gate_col >= 0) v *= 1.0f / (1.0f + expf(-to_f32(pr[row_gate_col])));
+    out[r * ld_out + i] = from_f32<T>(v);
+}
+
+__global__ void add_row_bias_kernel(float* __restrict__ x, const float* __restrict__ bias, long long n, int size) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] += bias[i % size];
+}
+
+__global__ void softcap_f32_kernel(float* __restrict__ x, long long n, float cap) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = cap * tanhf(x[i] / cap);
+}
+}  // namespace
+
+extern "C" int kipp_glu_limited(void* out, long long ld_out, const void* proj, long long ld_proj, int dtype, int rows, int n,
+                                int gate_off, int up_off, int step, const float* bias_gate, const float* bias_up,
+                                float limit, float alpha, int row_gate_col, void* stream) {
+    if (rows <= 0 || n <= 0) return 0;
+    if (step <= 0 || gate_off < 0 || up_off < 0) return KIPP_ERR_ARG;
+    const long long total = (long long)rows * n, blocks = (total + 255) / 256;
+    if (blocks > 0x7fffffffLL) return KIPP_ERR_ARG;
+    if (dtype == KIPP_DT_F32)
+        return kipp_launch(glu_limited_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, 1, (float*)out,
+                           ld_out, (const float*)proj, ld_proj, rows, n, gate_off, up_off, step, bias_gate, bias_up, limit,
+                           alpha, row_gate_col);
+    if (dtype == KIPP_DT_BF16)
+        return kipp_launch(glu_limited_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, 1, (bf16*)out,
+                           ld_out, (const bf16*)proj, ld_proj, rows, n, gate_off, up_off, step, bias_gate, bias_up, limit,
+                           alpha, row_gate_col);
+    return KIPP_ERR_DTYPE;
+}
+
+// x[r, :] += bias over rows of `size` float32 values.
+extern "C" int kipp_add_row_bias(float* x, const float* bias, int rows, int size, void* stream) {
+    if (rows <= 0 || size <= 0) return 0;
+    const long long n = (long long)rows * size, blocks = (n + 255) / 256;
+    if (blocks > 0x7fffffffLL || bias == nullptr) return KIPP_ERR_ARG;
+    return kipp_launch(add_row_bias_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, 1, x, bias, n, size);
+}
+
+// x <- cap * tanh(x / cap) over n float32 values (logits with a soft cap).
+extern "C" int kipp_softcap_f32(float* x, long long n, float cap, void* stream) {
+    if (n <= 0) return 0;
+    const long long blocks = (n + 255) / 256;
+    if (blocks > 0x7fffffffLL || !(cap > 0.f)) return KIPP_ERR_ARG;
+    return kipp_launch(softcap_f32_kernel, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, 1, x, n, cap);
+}

@@ -20,6 +20,7 @@
 #include "varunex.hpp"
 #include "expert_parts.hpp"
 #include "zasudra.hpp"
+#include "zunilorn.hpp"
 
 namespace kipp {
 
@@ -404,6 +405,7 @@ inline void AttentionMixer::forward(StepContext& ctx, const LayerRun& run, int m
             ops.qk_norm_rope_write(qkv, qkv_cols, q, cache, ctx.dtype, qn, kn, norm_dtype_, eps_, cos_sin, rot, m.positions,
                                    m.entry_of_token, T, heads_, kv_heads_, head_dim_, write, v_dim_);
         }
+        extras.softcap = (float)opt_.softcap;
         const int* tiles = nullptr;
         int n_tiles = 0;
         if (mix_planner_) {
@@ -584,7 +586,7 @@ inline size_t Engine::workspace_estimate() const {
     // feed-forward's activation (sizes are not known here per part: four hidden-wide rows of
     // slack stand for them), and the logits rows
     const size_t es = dtype_size(dtype_);
-    const size_t per_token = (size_t)plan_->hidden_size * (4 + es * 12);
+    const size_t per_token = (size_t)plan_->hidden_size * (4 * (size_t)(plan_->streams + (plan_->streams > 1 ? 2 : 0)) + es * 12);
     return per_token * (size_t)opt_.max_batch_tokens + (size_t)opt_.max_logit_rows * plan_->vocab_size * 4 + (64u << 20);
 }
 
@@ -931,8 +933,14 @@ inline const float* Engine::forward(StepMeta& meta) {
     ctx.kv_round_bf16 = opt_.kv_round_bf16 != 0;
     const long long before = ops_.launches;
     const int T = meta.shape.tokens;
-    float* x = workspace_.get<float>("residual", (size_t)T * plan_->hidden_size);
+    // (a plan with several copies of the residual stream: [streams][T, hidden], all equal at the start)
+    const int streams = plan_->streams;
+    const size_t one_stream = (size_t)T * plan_->hidden_size;
+    float* x = workspace_.get<float>("residual", one_stream * (size_t)streams);
     for (auto& e : plan_->embedding) e.second->forward(ctx, x);
+    for (int s = 1; s < streams; ++s)
+        cuda_check(cudaMemcpyAsync(x + (size_t)s * one_stream, x, one_stream * sizeof(float), cudaMemcpyDeviceToDevice, stream_),
+                   "copying the embedding output to a stream");
     // a run that adds the embedding output to the stream needs it kept
     float* embedded = nullptr;
     for (auto& run : plan_->order)
@@ -955,6 +963,11 @@ inline const float* Engine::forward(StepMeta& meta) {
     const int rows = meta.shape.logit_rows;
     if (rows > 0) {
         void* h = workspace_.buffer("final_normed", (size_t)rows * plan_->hidden_size * dtype_size(dtype_));
+        if (streams > 1) {                        // the model's output is the sum of the copies
+            float* sum = workspace_.get<float>("residual_sum", one_stream);
+            ops_.sum_streams(sum, x, (long long)one_stream, streams, (long long)one_stream);
+            x = sum;
+        }
         plan_->final_norm.second->forward(ctx, x, h, meta.logit_rows, rows);
         float* out = workspace_.get<float>("logits", (size_t)rows * plan_->vocab_size);
         plan_->head.second->forward(ctx, h, rows, out);
@@ -1181,11 +1194,15 @@ inline void Engine::debug_part(const StepEntryView* entries, int n, int run_inde
     };
     ParallelBlock* shared_norm = dynamic_cast<ParallelBlock*>(block);
     OutputNormBlock* out_norm = dynamic_cast<OutputNormBlock*>(block);
+    HyperConnectionBlock* hyper = dynamic_cast<HyperConnectionBlock*>(block);
     if (which == "embedding") {
         for (auto& e : plan_->embedding) e.second->forward(ctx, residual);
     } else if (which == "feed_forward" && out_norm != nullptr) {
         if (out_norm->feed_forward() == nullptr) fail(KIPP_E_ARGUMENT, "the block has no feed-forward");
         out_norm->feed_forward()->forward(ctx, input, residual);
+    } else if (which == "feed_forward" && hyper != nullptr) {
+        if (hyper->feed_forward() == nullptr) fail(KIPP_E_ARGUMENT, "the block has no feed-forward");
+        hyper->feed_forward()->forward(ctx, input, residual);
     } else if (which == "input_norm" && shared_norm != nullptr) {
         shared_norm->norm()->forward(ctx, residual, output, nullptr, T);
     } else if (which == "feed_forward" && shared_norm != nullptr) {

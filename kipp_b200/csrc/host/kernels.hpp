@@ -89,7 +89,8 @@ struct AttentionExtras {
     long long ld_gate = 0;
     int gate_off = 0;
     int chunk = 0;                         // > 0: a query sees the keys j <= p of its own block of `chunk` positions
-    bool any() const { return sink || key_maps != 1 || values_in_keys || diff || gate || chunk; }
+    float softcap = 0.f;                   // > 0: a scaled score s becomes softcap * tanh(s / softcap)
+    bool any() const { return sink || key_maps != 1 || values_in_keys || diff || gate || chunk || softcap > 0.f; }
 };
 
 // A run of heads in a projection row and what becomes of them (the layout is the kernel
@@ -253,6 +254,14 @@ public:
         using Fn = int (*)(void*, const int*, const float*, int, int, void*);
         static Fn f = kernel_symbol<Fn>("rope_cache", "kipp_rope_table_by_pair");
         run(f(out, positions, inv_freq, tokens, half, stream), "rope_table");
+    }
+
+    // The step's table with cos and sin both multiplied by `magnitude`.
+    void rope_table_scaled(float* out, const int* positions, const float* inv_freq, int tokens, int half, bool by_pair,
+                           float magnitude) {
+        using Fn = int (*)(void*, const int*, const float*, int, int, int, float, void*);
+        static Fn f = kernel_symbol<Fn>("rope_cache", "kipp_rope_table_scaled");
+        run(f(out, positions, inv_freq, tokens, half, by_pair ? 1 : 0, magnitude, stream), "rope_table");
     }
 
     // Per-head RMSNorm of q and k, rotation, q to q_out [T, n_q, D], k and v into the pages.
@@ -493,6 +502,50 @@ public:
         static Fn f = kernel_symbol<Fn>("elementwise", "kipp_rmsnorm_scaled_add");
         run(f(x, y, w, w_dtype, rows, size, eps, mult, copy_bf16, stream), "rmsnorm_scaled_add");
     }
+    // Hyper-connections (elementwise.cu): the residual stream as `streams` copies, `stride` floats apart.
+    // y given: x_t <- sum_s mix[s, t] x_s + mult out_w[t] y; h given: h = rmsnorm(sum_s in_w[s] x_s).
+    static int hyper_connection_max_streams() {
+        using Fn = int (*)();
+        static Fn f = kernel_symbol<Fn>("elementwise", "kipp_hyper_connection_max_streams");
+        return f();
+    }
+    void hyper_connection(float* x, long long stride, int streams, const float* y, const float* mix, const float* out_w,
+                          float mult, const float* in_w, const void* norm_w, int norm_w_dtype, float eps, void* h,
+                          int h_dtype, int rows, int size) {
+        using Fn = int (*)(float*, long long, int, const float*, const float*, const float*, float, const float*, const void*,
+                           int, float, void*, int, int, int, void*);
+        static Fn f = kernel_symbol<Fn>("elementwise", "kipp_hyper_connection");
+        run(f(x, stride, streams, y, mix, out_w, mult, in_w, norm_w, norm_w_dtype, eps, h, h_dtype, rows, size, stream),
+            "hyper_connection");
+    }
+    void sum_streams(float* out, const float* x, long long stride, int streams, long long n) {
+        using Fn = int (*)(float*, const float*, long long, int, long long, void*);
+        static Fn f = kernel_symbol<Fn>("elementwise", "kipp_sum_streams");
+        run(f(out, x, stride, streams, n, stream), "sum_streams");
+    }
+    // out[r, i] = g sigmoid(alpha g) (u + 1), g = min(gate + bg, limit), u = clamp(up + bu, -limit, limit); gate of
+    // element i at proj[r, gate_off + i * step], up at proj[r, up_off + i * step]; row_gate_col >= 0: the row is
+    // also multiplied by sigmoid(proj[r, row_gate_col]).
+    void glu_limited(void* out, long long ld_out, const void* proj, long long ld_proj, int dtype, int rows, int n, int gate_off,
+                     int up_off, int step, const float* bias_gate, const float* bias_up, float limit, float alpha,
+                     int row_gate_col) {
+        using Fn = int (*)(void*, long long, const void*, long long, int, int, int, int, int, int, const float*, const float*,
+                           float, float, int, void*);
+        static Fn f = kernel_symbol<Fn>("elementwise", "kipp_glu_limited");
+        run(f(out, ld_out, proj, ld_proj, dtype, rows, n, gate_off, up_off, step, bias_gate, bias_up, limit, alpha, row_gate_col,
+              stream),
+            "glu_limited");
+    }
+    void add_row_bias(float* x, const float* bias, int rows, int size) {
+        using Fn = int (*)(float*, const float*, int, int, void*);
+        static Fn f = kernel_symbol<Fn>("elementwise", "kipp_add_row_bias");
+        run(f(x, bias, rows, size, stream), "add_row_bias");
+    }
+    void softcap_f32(float* x, long long n, float cap) {
+        using Fn = int (*)(float*, long long, float, void*);
+        static Fn f = kernel_symbol<Fn>("elementwise", "kipp_softcap_f32");
+        run(f(x, n, cap, stream), "softcap_f32");
+    }
     void scale_f32(float* x, long long n, float scale) {
         using Fn = int (*)(float*, long long, float, void*);
         static Fn f = kernel_symbol<Fn>("elementwise", "kipp_scale_f32");
@@ -536,6 +589,54 @@ public:
         run(f(out, ld_out, proj, ld_proj, dtype, r_off, k_off, v_off, g_off, w_raw, ld_w, w_bias, bonus, norm_w, state,
               slot_stride, q_start, slots, entries, tokens, heads, dim, eps, out_scale, gate, scratch, stream),
             "wkv_scan", 3);
+    }
+
+    // The state space layer (recurrent.cu, kind 4): convolution, dt, the recurrence, gate and grouped norm.
+    static bool ssd_ok(int dim, int v_dim) {
+        using Fn = int (*)(int, int, int);
+        static Fn f = kernel_symbol<Fn>("recurrent", "kipp_recurrent_scan_ok");
+        return f(dim, v_dim, 4) != 0;
+    }
+    static long long ssd_state_floats(int heads, int groups, int dim, int v_dim, int taps) {
+        using Fn = long long (*)(int, int, int, int, int);
+        static Fn f = kernel_symbol<Fn>("recurrent", "kipp_ssd_state_floats");
+        return f(heads, groups, dim, v_dim, taps);
+    }
+    void ssd_scan(void* out, long long ld_out, const void* proj, long long ld_proj, int dtype, int z_off, int xbc_off,
+                  int dt_off, const float* conv_w, const float* conv_b, int taps, const float* dt_bias, const float* a_log,
+                  const float* d_skip, const float* norm_w, int norm_groups, float* state, long long slot_stride,
+                  const int* q_start, const int* entry_of_token, const int* slots, int entries, int tokens, int heads,
+                  int groups, int dim, int v_dim, float eps) {
+        using Fn = int (*)(void*, long long, const void*, long long, int, int, int, int, const float*, const float*, int,
+                           const float*, const float*, const float*, const float*, int, float*, long long, const int*,
+                           const int*, const int*, int, int, int, int, int, int, float, float*, void*);
+        static Fn f = kernel_symbol<Fn>("recurrent", "kipp_ssd_scan");
+        float* scratch = recurrent_scratch(tokens, heads, dim, v_dim, 4);
+        run(f(out, ld_out, proj, ld_proj, dtype, z_off, xbc_off, dt_off, conv_w, conv_b, taps, dt_bias, a_log, d_skip, norm_w,
+              norm_groups, state, slot_stride, q_start, entry_of_token, slots, entries, tokens, heads, groups, dim, v_dim, eps,
+              scratch, stream),
+            "ssd_scan", taps > 1 ? 4 : 3);
+    }
+
+    // Routing by scores (moe.cu): softmax over all `outputs`, the choice by score + correction, weights
+    // score / sum of the chosen x weight_scale; outputs from `experts` on are identity experts (negative ids).
+    void moe_route_scores(int* expert_of, float* weight_of, const void* h, long long ldh, int dtype, const float* router,
+                          const float* correction, int tokens, int hidden, int outputs, int experts, int top,
+                          float weight_scale) {
+        using Fn = int (*)(int*, float*, const void*, long long, int, const float*, const float*, int, int, int, int, int, float,
+                           void*);
+        static Fn f = kernel_symbol<Fn>("moe", "kipp_moe_route_scores");
+        run(f(expert_of, weight_of, h, ldh, dtype, router, correction, tokens, hidden, outputs, experts, top, weight_scale,
+              stream),
+            "moe_route");
+    }
+    // The combine where pairs with a negative expert id stand for the token's own input h.
+    void moe_combine_identity(float* y, const float* rows, const float* weight_of, const int* expert_of, const void* h,
+                              long long ldh, int dtype, int tokens, int hidden, int top, const int* place_of_pair = nullptr) {
+        using Fn = int (*)(float*, const float*, const float*, const int*, const void*, long long, int, int, int, int,
+                           const int*, void*);
+        static Fn f = kernel_symbol<Fn>("moe", "kipp_moe_combine_identity");
+        run(f(y, rows, weight_of, expert_of, h, ldh, dtype, tokens, hidden, top, place_of_pair, stream), "moe_combine");
     }
 
     // Routed experts (moe.cu).  route: the `top` largest of z = W_r h + b per token (float32) and the

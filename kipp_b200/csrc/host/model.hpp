@@ -210,6 +210,7 @@ public:
     virtual int rotary_dim() const = 0;
     virtual const float* inv_freq_device() const = 0;     // float32 [rotary_dim / 2], after bind
     virtual std::string table_key() const = 0;            // encodings with equal keys share a step's (cos, sin) table
+    virtual float magnitude() const { return 1.f; }       // a factor on cos and sin both (rotations that also stretch)
 };
 
 class Mixer : public Part {
@@ -258,11 +259,16 @@ public:
     // the norm the block applies to the residual stream first, if the part after it takes its
     // input in deferred form (see StepContext::input_scale)
     virtual const Norm* deferred_first_norm() const { return nullptr; }
+    // Copies of the residual stream the block works on (hyper-connections): x is then
+    // [streams][T, hidden], the copies T * hidden floats apart.  Every block of a plan agrees with
+    // the plan's `streams`.
+    virtual int streams() const { return 1; }
 };
 
 // ---------------------------------------------------------------------------------------------
 struct ModelPlan {
     int hidden_size = 0, vocab_size = 0;
+    int streams = 1;                                                    // copies of the residual stream (hyper-connections)
     long long max_positions = 0;                                        // 0: no limit of the model's own
     Json config;                                                        // the configuration it was built from
     std::vector<std::pair<std::string, std::unique_ptr<EmbeddingStage>>> embedding;
@@ -356,7 +362,7 @@ private:
 };
 
 void register_builtin_parts();           // parts.hpp, recurrent_parts.hpp, latent_parts.hpp, expert_parts.hpp
-void register_builtin_architectures();   // qwen3.hpp, venizen.hpp, varunex.hpp, zasudra.hpp
+void register_builtin_architectures();   // qwen3.hpp, venizen.hpp, varunex.hpp, zasudra.hpp, zunilorn.hpp
 
 inline void ensure_registered() {
     static std::once_flag once;
@@ -384,6 +390,7 @@ inline std::unique_ptr<ModelPlan> build_plan(const Json& j, const BuildContext& 
         plan->hidden_size = (int)j.get("hidden_size").as_int();
         plan->vocab_size = (int)j.get("vocab_size").as_int();
         plan->max_positions = j.get_int("max_positions", 0);
+        plan->streams = (int)j.get_int("streams", 1);
         if (const Json* c = j.find("config")) plan->config = *c;
         for (auto& e : j.get("embedding").items())
             plan->embedding.emplace_back(e.get_string("prefix", ""),
@@ -410,6 +417,11 @@ inline std::unique_ptr<ModelPlan> build_plan(const Json& j, const BuildContext& 
         fail(KIPP_E_CONFIG, std::string("the model plan is malformed: ") + e.what());
     }
     if (plan->hidden_size <= 0 || plan->vocab_size <= 0) fail(KIPP_E_CONFIG, "the plan's sizes must be positive");
+    if (plan->streams < 1) fail(KIPP_E_CONFIG, "the plan's 'streams' must be at least 1");
+    for (auto& l : plan->layers)
+        if (l.second->streams() != plan->streams)
+            fail(KIPP_E_CONFIG, format("a block works on %d copies of the residual stream, the plan has %d",
+                                       l.second->streams(), plan->streams));
     return plan;
 }
 

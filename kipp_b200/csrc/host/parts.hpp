@@ -84,10 +84,12 @@ private:
 // head of its own (src/kipp.c:951-956, 3013-3018).
 class OutputHead : public Head {
 public:
-    OutputHead(int vocab, int hidden, std::string tied_to, std::string weight_name = "weight", double logit_scale = 1.0)
+    OutputHead(int vocab, int hidden, std::string tied_to, std::string weight_name = "weight", double logit_scale = 1.0,
+               double logit_softcap = 0.0)
         : vocab_(vocab), hidden_(hidden), tied_to_(std::move(tied_to)), name_(std::move(weight_name)),
-          scale_((float)logit_scale) {
+          scale_((float)logit_scale), softcap_((float)logit_softcap) {
         if (vocab <= 0 || hidden <= 0) fail(KIPP_E_CONFIG, "output_head: sizes must be positive");
+        if (logit_softcap < 0) fail(KIPP_E_CONFIG, "output_head: logit_softcap must not be negative");
     }
     void tensor_specs(const std::string& prefix, std::vector<TensorSpec>& out) const override {
         TensorSpec s;
@@ -109,12 +111,14 @@ public:
     void forward(StepContext& ctx, const void* h, int n_rows, float* logits) override {
         ctx.ops->gemm(logits, F32, vocab_, h, hidden_, weight_, hidden_, dtype_, n_rows, vocab_, hidden_, EPI_STORE);
         if (scale_ != 1.0f) ctx.ops->scale_f32(logits, (long long)n_rows * vocab_, scale_);     // logit_scale, in float32
+        // logit_softcap c > 0: logits <- c tanh(logits / c), in float32
+        if (softcap_ > 0.f) ctx.ops->softcap_f32(logits, (long long)n_rows * vocab_, softcap_);
     }
 
 private:
     int vocab_, hidden_, dtype_ = BF16;
     std::string tied_to_, name_;
-    float scale_ = 1.f;
+    float scale_ = 1.f, softcap_ = 0.f;
     void* weight_ = nullptr;
 };
 
@@ -199,8 +203,10 @@ private:
 // position * inv_freq[i].
 class FrequencyTable : public PositionEncoding {
 public:
-    FrequencyTable(std::vector<float> inv_freq, std::string key) : freq_(std::move(inv_freq)), key_(std::move(key)) {}
+    FrequencyTable(std::vector<float> inv_freq, std::string key, float magnitude = 1.f)
+        : freq_(std::move(inv_freq)), key_(std::move(key)), magnitude_(magnitude) {}
     int rotary_dim() const override { return 2 * (int)freq_.size(); }
+    float magnitude() const override { return magnitude_; }
     const float* inv_freq_device() const override { return device_; }
     std::string table_key() const override { return key_; }
     void bind(Binder& b, const std::string&) override {
@@ -214,6 +220,7 @@ public:
 private:
     std::vector<float> freq_;
     std::string key_;
+    float magnitude_ = 1.f;
     float* device_ = nullptr;
 };
 
@@ -253,6 +260,29 @@ inline std::vector<float> stretched_frequencies(int rotary_dim, double theta, do
     }
     return f;
 }
+
+// Frequencies scaled by a ramp over the pair index (the YaRN way of stretching a context): with
+// pair(t) = dims ln(original / (2 pi t)) / (2 ln theta) the (real) pair index that makes t turns within
+// `original` positions, lo = max(floor(pair(fast)), 0), hi = min(ceil(pair(slow)), dims - 1) and
+// ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1), the frequency of pair i is
+// f_i / factor * ramp_i + f_i (1 - ramp_i): pairs that turn fast stay, slow ones are divided by the
+// factor.  cos and sin are both multiplied by 0.1 ln(factor) + 1 (yarn_magnitude).  Formed in double
+// precision, rounded to float32 once.
+inline std::vector<float> yarn_frequencies(int rotary_dim, double theta, double factor, double original, double fast,
+                                           double slow) {
+    std::vector<float> f((size_t)rotary_dim / 2);
+    const double two_pi = 6.283185307179586476925286766559;
+    auto pair_of = [&](double turns) { return rotary_dim * std::log(original / (two_pi * turns)) / (2.0 * std::log(theta)); };
+    const double lo = std::max(std::floor(pair_of(fast)), 0.0);
+    const double hi = std::min(std::ceil(pair_of(slow)), (double)rotary_dim - 1.0);
+    for (int i = 0; i < rotary_dim / 2; ++i) {
+        const double v = std::pow(theta, -2.0 * (double)i / (double)rotary_dim);
+        const double ramp = std::min(std::max(((double)i - lo) / std::max(hi - lo, 0.001), 0.0), 1.0);
+        f[(size_t)i] = (float)(v / factor * ramp + v * (1.0 - ramp));
+    }
+    return f;
+}
+inline float yarn_magnitude(double factor) { return (float)(0.1 * std::log(factor) + 1.0); }
 
 // ---------------------------------------------------------------------------------------------
 // The work lists of the paged attention kernels and the rule for the decode splits.  The
@@ -474,7 +504,9 @@ inline const float* step_rope_table(StepContext& ctx, const PositionEncoding& po
         int made = 0;
         for (auto& kv : ctx.step_cache) made += kv.first.rfind("rope", 0) == 0;
         float* table = ctx.workspace->get<float>("rope_table_" + std::to_string(made), (size_t)T * rot);
-        if (by_pair) ctx.ops->rope_table_by_pair(table, ctx.meta->positions, position.inv_freq_device(), T, rot / 2);
+        if (position.magnitude() != 1.f)
+            ctx.ops->rope_table_scaled(table, ctx.meta->positions, position.inv_freq_device(), T, rot / 2, by_pair, position.magnitude());
+        else if (by_pair) ctx.ops->rope_table_by_pair(table, ctx.meta->positions, position.inv_freq_device(), T, rot / 2);
         else ctx.ops->rope_table(table, ctx.meta->positions, position.inv_freq_device(), T, rot / 2);
         it = ctx.step_cache.emplace(key, table).first;
     }
@@ -518,7 +550,8 @@ inline std::map<std::string, std::string> tensor_names(const Json& j, std::map<s
 // denominator, learned per head or of score 0 (sink); a sigmoid gate per head from a projection of
 // the mixer's input (head_gate); values that are the keys as projected (values_are_keys: no W_v);
 // and a mixer without keys and values of its own that reads what another run wrote (shared_kv:
-// the run order gives it that run's cache id and writes_cache false).
+// the run order gives it that run's cache id and writes_cache false).  A cap on the scaled scores
+// (softcap c: s <- c tanh(s / c)) goes with every option of this path.
 struct AttentionOptions {
     int value_dim = 0, keep_first = 0;
     bool head_mix = false;
@@ -534,6 +567,7 @@ struct AttentionOptions {
     bool head_gate = false;             // head h times sigmoid(W_g h)_h, W_g [heads, hidden]
     bool values_are_keys = false;       // no W_v: the value of a key is the key as projected (before norm and rotation)
     bool shared_kv = false;             // no keys and values of its own: the run reads the cache another run wrote
+    double softcap = 0.0;               // > 0: a scaled score s becomes softcap * tanh(s / softcap) before mask and softmax
     std::map<std::string, std::string> names = {{"q", "q_proj.weight"}, {"k", "k_proj.weight"}, {"v", "v_proj.weight"},
                                                 {"o", "o_proj.weight"}, {"q_norm", "q_norm.weight"},
                                                 {"k_norm", "k_norm.weight"}, {"head_mix", "head_mix.weight"},
@@ -586,8 +620,9 @@ public:
         g_cols_ = opt_.head_gate ? heads : 0;
         proj_cols_ = q_dim_ + k_cols_ + v_cols_ + g_cols_;
         proj_ld_ = more ? (proj_cols_ + 7) / 8 * 8 : proj_cols_;
+        if (opt_.softcap < 0) fail(KIPP_E_CONFIG, "attention: softcap must not be negative");
         mix_path_ = opt_.head_mix || (window_ > 0 && opt_.keep_first > 0) || v_dim_ != head_dim_ ||
-                    opt_.output_scale != 1.0 || segments_;
+                    opt_.output_scale != 1.0 || segments_ || opt_.softcap > 0;
     }
     void tensor_specs(const std::string& p, std::vector<TensorSpec>& out) const override {
         auto add = [&](const char* role, std::vector<int64_t> shape, const char* init = "normal") {
@@ -835,6 +870,98 @@ private:
     void *w_up_ = nullptr, *w_down_ = nullptr;
 };
 
+// Gated dense feed-forward with limits: g = min(W_gate n + b_g, limit), u = clamp(W_up n + b_u, -limit, limit),
+// x += W_down (g sigmoid(alpha g) (u + 1)) + b_d.  Biases are optional (bias), limit 0 means none.  With
+// row_gate the part's output is also multiplied by sigmoid(w_r . n), one number per token (a tensor
+// [1, hidden]): the factor is applied to the hidden row before the (linear) down projection.  One product
+// makes gate, up and the row gate; the activation runs in float32.
+class GatedFeedForward : public FeedForward {
+public:
+    explicit GatedFeedForward(const Json& j) {
+        hidden_ = (int)j.get("hidden_size").as_int();
+        inter_ = (int)j.get("intermediate_size").as_int();
+        limit_ = (float)j.get_double("limit", 0.0);
+        alpha_ = (float)j.get_double("alpha", 1.0);
+        bias_ = j.get_bool("bias", false);
+        row_gate_ = j.get_bool("row_gate", false);
+        names_ = tensor_names(j, {{"gate", "gate"}, {"up", "up"}, {"down", "down"}, {"gate_bias", "gate.b"},
+                                  {"up_bias", "up.b"}, {"down_bias", "down.b"}, {"row_gate", "sg"}});
+        if (hidden_ <= 0 || inter_ <= 0) fail(KIPP_E_CONFIG, "gated_mlp: sizes must be positive");
+        if (limit_ < 0.f) fail(KIPP_E_CONFIG, "gated_mlp: limit must not be negative");
+        inter_ld_ = (inter_ + 7) / 8 * 8;
+        proj_cols_ = 2 * inter_ld_ + (row_gate_ ? 1 : 0);        // gate and up each start on a 16-byte boundary of the row
+        proj_ld_ = (proj_cols_ + 7) / 8 * 8;
+    }
+    void tensor_specs(const std::string& p, std::vector<TensorSpec>& out) const override {
+        auto add = [&](const char* role, std::vector<int64_t> shape) {
+            TensorSpec s;
+            s.name = p + names_.at(role);
+            s.shape = std::move(shape);
+            out.push_back(s);
+        };
+        add("gate", {inter_, hidden_});
+        add("up", {inter_, hidden_});
+        add("down", {hidden_, inter_});
+        if (bias_) {
+            add("gate_bias", {inter_});
+            add("up_bias", {inter_});
+            add("down_bias", {hidden_});
+        }
+        if (row_gate_) add("row_gate", {1, hidden_});
+    }
+    void bind(Binder& b, const std::string& p) override {
+        dtype_ = b.compute_dtype();
+        const size_t es = dtype_size(dtype_);
+        w_in_ = b.allocate((size_t)proj_cols_ * hidden_ * es, p + "gate, up");
+        cuda_check(cudaMemset(w_in_, 0, (size_t)proj_cols_ * hidden_ * es), "clearing a padded weight");
+        char* base = static_cast<char*>(w_in_);
+        b.load(p + names_.at("gate"), base, dtype_, hidden_, inter_, hidden_);
+        b.load(p + names_.at("up"), base + (size_t)inter_ld_ * hidden_ * es, dtype_, hidden_, inter_, hidden_);
+        if (row_gate_) b.load(p + names_.at("row_gate"), base + (size_t)2 * inter_ld_ * hidden_ * es, dtype_, hidden_, 1, hidden_);
+        w_down_ = b.allocate((size_t)hidden_ * inter_ld_ * es, p + names_.at("down"));
+        cuda_check(cudaMemset(w_down_, 0, (size_t)hidden_ * inter_ld_ * es), "clearing a padded weight");
+        b.load(p + names_.at("down"), w_down_, dtype_, inter_ld_, hidden_, inter_);
+        if (bias_) {
+            auto floats = [&](const char* role, int64_t n) {
+                float* d = static_cast<float*>(b.allocate((size_t)n * sizeof(float), p + names_.at(role)));
+                b.load(p + names_.at(role), d, F32, n, 1, n);
+                return d;
+            };
+            b_gate_ = floats("gate_bias", inter_);
+            b_up_ = floats("up_bias", inter_);
+            b_down_ = floats("down_bias", hidden_);
+        }
+    }
+    size_t weight_bytes() const override {
+        return ((size_t)3 * inter_ + (row_gate_ ? 1 : 0)) * hidden_ * dtype_size(dtype_) + (bias_ ? (size_t)(2 * inter_ + hidden_) * 4 : 0);
+    }
+    bool folds_rms() const override { return Ops::gemm_scale_ok(dtype_, w_in_, hidden_, w_in_, hidden_); }
+    void forward(StepContext& ctx, const void* h, float* residual) override {
+        const int T = ctx.tokens();
+        NormFold in, out;
+        void* proj = ctx.workspace->buffer("gated_mlp_proj", (size_t)T * proj_ld_ * ctx.element());
+        ctx.ops->gemm(proj, ctx.dtype, proj_ld_, h, hidden_, w_in_, hidden_, dtype_, T, proj_cols_, hidden_, EPI_STORE,
+                      fold_input(ctx, in));
+        void* act = ctx.workspace->buffer("gated_mlp_act", (size_t)T * inter_ld_ * ctx.element());
+        if (inter_ld_ != inter_) cuda_check(cudaMemsetAsync(act, 0, (size_t)T * inter_ld_ * ctx.element(), ctx.stream), "clearing the padding");
+        ctx.ops->glu_limited(act, inter_ld_, proj, proj_ld_, ctx.dtype, T, inter_, 0, inter_ld_, 1, b_gate_, b_up_, limit_, alpha_,
+                             row_gate_ ? 2 * inter_ld_ : -1);
+        const NormFold* emit = fold_emit(ctx, out, hidden_);
+        ctx.ops->gemm(residual, F32, hidden_, act, inter_ld_, w_down_, inter_ld_, dtype_, T, hidden_, inter_ld_, EPI_ADD, emit);
+        if (b_down_ != nullptr && emit != nullptr) fail(KIPP_E_STATE, "gated_mlp: a bias on the output does not go with an emitted norm");
+        fold_emitted(ctx, emit, hidden_);
+        if (b_down_ != nullptr) ctx.ops->add_row_bias(residual, b_down_, T, hidden_);
+    }
+
+private:
+    int hidden_ = 0, inter_ = 0, inter_ld_ = 0, proj_cols_ = 0, proj_ld_ = 0, dtype_ = BF16;
+    float limit_ = 0.f, alpha_ = 1.f;
+    bool bias_ = false, row_gate_ = false;
+    std::map<std::string, std::string> names_;
+    void *w_in_ = nullptr, *w_down_ = nullptr;
+    float *b_gate_ = nullptr, *b_up_ = nullptr, *b_down_ = nullptr;
+};
+
 // x += mixer(n) + ffn(n) with n = norm(x): ONE norm whose output both sublayers read.  A block
 // without a feed-forward (ffn null) has the mixer only.
 class ParallelBlock : public Block {
@@ -1058,6 +1185,131 @@ private:
     std::vector<std::string> names_;
 };
 
+// Hyper-connections: the residual stream is `streams` copies x_1 .. x_S (all equal to the embedding
+// output at the start, summed at the end).  Sublayer q (1 the mixer, 2 the feed-forward) reads
+// u = sum_s in_q[s] x_s through its RMS norm, and its output y joins every copy at once:
+// x_t <- sum_s mix_q[s, t] x_s + mult * out_q[t] * y.  Three small tensors per sublayer (in [S], out [S],
+// mix [S, S] indexed [from, to]) under the prefixes names[4], names[5].  Without connections
+// (connections false: no such tensors) the block is the plain pre-norm x <- x + mult * sublayer(norm(x))
+// on one stream.  The kernel between two sublayers updates the copies and forms the next sublayer's
+// input in one pass; everything of it is float32.  A block without a feed-forward has the mixer only.
+class HyperConnectionBlock : public Block {
+public:
+    HyperConnectionBlock(const Json& j, std::unique_ptr<Norm> n1, std::unique_ptr<Mixer> mixer, std::unique_ptr<Norm> n2,
+                         std::unique_ptr<FeedForward> ffn)
+        : n1_(std::move(n1)), mixer_(std::move(mixer)), n2_(std::move(n2)), ffn_(std::move(ffn)) {
+        streams_ = (int)j.get_int("streams", 1);
+        connections_ = j.get_bool("connections", true);
+        mult_ = (float)j.get_double("residual_mult", 1.0);
+        for (auto& n : j.get("names").items()) names_.push_back(n.as_string());
+        if (names_.size() != 6) fail(KIPP_E_CONFIG, "hyper_connection_block: six name prefixes are needed");
+        if (streams_ < 1) fail(KIPP_E_CONFIG, "hyper_connection_block: streams must be at least 1");
+        if (!connections_ && streams_ != 1) fail(KIPP_E_CONFIG, "hyper_connection_block: several streams need their connections");
+        if ((n2_ == nullptr) != (ffn_ == nullptr))
+            fail(KIPP_E_CONFIG, "hyper_connection_block: post_norm and ffn come together or not at all");
+        if (n2_ && n1_->size() != n2_->size()) fail(KIPP_E_CONFIG, "hyper_connection_block: the two norms differ in size");
+    }
+    int streams() const override { return streams_; }
+    void tensor_specs(const std::string& p, std::vector<TensorSpec>& out) const override {
+        n1_->tensor_specs(p + names_[0], out);
+        mixer_->tensor_specs(p + names_[1], out);
+        if (ffn_) {
+            n2_->tensor_specs(p + names_[2], out);
+            ffn_->tensor_specs(p + names_[3], out);
+        }
+        if (!connections_) return;
+        for (int q = 0; q < (ffn_ ? 2 : 1); ++q) {
+            auto add = [&](const char* name, std::vector<int64_t> shape, const char* init) {
+                TensorSpec s;
+                s.name = p + names_[4 + (size_t)q] + name;
+                s.shape = std::move(shape);
+                s.init = init;
+                out.push_back(s);
+            };
+            add("in", {streams_}, "near_one");
+            add("out", {streams_}, "near_one");
+            add("mix", {streams_, streams_}, "near_identity");
+        }
+    }
+    void bind(Binder& b, const std::string& p) override {
+        n1_->bind(b, p + names_[0]);
+        mixer_->bind(b, p + names_[1]);
+        if (ffn_) {
+            n2_->bind(b, p + names_[2]);
+            ffn_->bind(b, p + names_[3]);
+        }
+        if (!n1_->rms_spec() || (n2_ && !n2_->rms_spec()))
+            fail(KIPP_E_CONFIG, "hyper_connection_block: the norms must be RMS norms");
+        if (streams_ > Ops::hyper_connection_max_streams())
+            fail(KIPP_E_UNSUPPORTED, format("hyper_connection_block: at most %d streams", Ops::hyper_connection_max_streams()));
+        if (!connections_) return;
+        // in [S], out [S], mix [S, S] of each sublayer, float32, one after another
+        const size_t per = (size_t)streams_ * (streams_ + 2);
+        coef_ = static_cast<float*>(b.allocate(2 * per * sizeof(float), p + "connections"));
+        for (int q = 0; q < (ffn_ ? 2 : 1); ++q) {
+            float* c = coef_ + (size_t)q * per;
+            const std::string hp = p + names_[4 + (size_t)q];
+            b.load(hp + "in", c, F32, streams_, 1, streams_);
+            b.load(hp + "out", c + streams_, F32, streams_, 1, streams_);
+            b.load(hp + "mix", c + 2 * streams_, F32, streams_, streams_, streams_);
+        }
+    }
+    size_t weight_bytes() const override {
+        return n1_->weight_bytes() + mixer_->weight_bytes() + (ffn_ ? n2_->weight_bytes() + ffn_->weight_bytes() : 0) +
+               (connections_ ? (size_t)2 * streams_ * (streams_ + 2) * 4 : 0);
+    }
+    bool graph_safe() const override {
+        return n1_->graph_safe() && mixer_->graph_safe() && (!ffn_ || (n2_->graph_safe() && ffn_->graph_safe()));
+    }
+    std::vector<Mixer*> mixers() override { return mixer_->parts(); }
+    void forward(StepContext& ctx, const LayerRun& run, float* x) override {
+        const int T = ctx.tokens(), W = n1_->size(), S = streams_;
+        const long long stride = (long long)T * W;
+        Ops& ops = *ctx.ops;
+        // the norms run inside the connection kernel: nothing to fold into the products, nothing pending
+        ctx.input_scale = RowScale{};
+        ctx.pending_norm = nullptr;
+        ctx.emit_for = nullptr;
+        ctx.emitted = false;
+        void* h = ctx.workspace->buffer("normed", (size_t)T * W * ctx.element());
+        float* y = ctx.workspace->get<float>("sublayer_output", (size_t)T * W);
+        const size_t per = (size_t)S * (S + 2);
+        auto in_w = [&](int q) { return connections_ ? coef_ + (size_t)q * per : nullptr; };
+        auto out_w = [&](int q) { return connections_ ? coef_ + (size_t)q * per + S : nullptr; };
+        auto mix = [&](int q) { return connections_ ? coef_ + (size_t)q * per + 2 * S : nullptr; };
+        const RmsNormSpec s1 = *n1_->rms_spec();
+        ops.hyper_connection(x, stride, S, nullptr, nullptr, nullptr, 0.f, in_w(0), s1.weight, s1.weight_dtype, s1.eps, h,
+                             ctx.dtype, T, W);
+        cuda_check(cudaMemsetAsync(y, 0, (size_t)T * W * sizeof(float), ctx.stream), "clearing a sublayer's output");
+        mixer_->forward(ctx, run, 0, h, y);
+        if (ffn_) {
+            const RmsNormSpec s2 = *n2_->rms_spec();
+            ops.hyper_connection(x, stride, S, y, mix(0), out_w(0), mult_, in_w(1), s2.weight, s2.weight_dtype, s2.eps, h,
+                                 ctx.dtype, T, W);
+            cuda_check(cudaMemsetAsync(y, 0, (size_t)T * W * sizeof(float), ctx.stream), "clearing a sublayer's output");
+            ffn_->forward(ctx, h, y);
+            ops.hyper_connection(x, stride, S, y, mix(1), out_w(1), mult_, nullptr, nullptr, 0, 0.f, nullptr, ctx.dtype, T, W);
+        } else {
+            ops.hyper_connection(x, stride, S, y, mix(0), out_w(0), mult_, nullptr, nullptr, 0, 0.f, nullptr, ctx.dtype, T, W);
+        }
+        ctx.emitted = false;
+    }
+    Norm* input_norm() { return n1_.get(); }
+    Norm* post_norm() { return n2_.get(); }
+    FeedForward* feed_forward() { return ffn_.get(); }
+
+private:
+    std::unique_ptr<Norm> n1_;
+    std::unique_ptr<Mixer> mixer_;
+    std::unique_ptr<Norm> n2_;
+    std::unique_ptr<FeedForward> ffn_;
+    int streams_ = 1;
+    bool connections_ = true;
+    float mult_ = 1.f;
+    std::vector<std::string> names_;
+    float* coef_ = nullptr;
+};
+
 // ---------------------------------------------------------------------------------------------
 // Parts whose forward pass the caller supplies (kipp_external_part).  The plan declares what
 // the engine has to know without calling them: their tensors (so that a checkpoint is checked
@@ -1237,7 +1489,7 @@ inline void register_builtin_parts() {
     r.add_part_kind("output_head", [](const Json& j, const BuildContext&) -> std::unique_ptr<Part> {
         return std::make_unique<OutputHead>((int)j.get("vocab_size").as_int(), (int)j.get("hidden_size").as_int(),
                                             j.get_string("tied_to", ""), j.get_string("weight_name", "weight"),
-                                            j.get_double("logit_scale", 1.0));
+                                            j.get_double("logit_scale", 1.0), j.get_double("logit_softcap", 0.0));
     });
     r.add_part_kind("hashed_pair_embedding", [](const Json& j, const BuildContext&) -> std::unique_ptr<Part> {
         return std::make_unique<HashedPairEmbedding>((int)j.get("vocab_size").as_int(), (int)j.get("hidden_size").as_int(),
@@ -1263,6 +1515,33 @@ inline void register_builtin_parts() {
             fail(KIPP_E_CONFIG, "stretched_rotary: theta, factor, low and original must be positive and high above low");
         return std::make_unique<FrequencyTable>(stretched_frequencies(rot, theta, factor, low, high, original),
                                                 format("stretched/%.17g/%d/%.17g/%.17g/%.17g/%.17g", theta, rot, factor, low, high, original));
+    });
+    r.add_part_kind("yarn_rotary", [](const Json& j, const BuildContext&) -> std::unique_ptr<Part> {
+        const int head_dim = (int)j.get("head_dim").as_int();
+        const int rot = (int)j.get_int("rotary_dim", head_dim);
+        const double theta = j.get("theta").as_double(), factor = j.get("factor").as_double();
+        const double original = j.get("original").as_double(), fast = j.get("fast").as_double(), slow = j.get("slow").as_double();
+        if (rot % 2 || rot <= 0 || rot > head_dim)
+            fail(KIPP_E_CONFIG, format("rotary_dim %d must be even, positive and at most head_dim %d", rot, head_dim));
+        if (!(theta > 0) || theta == 1.0 || !(factor > 0) || !(original > 0) || !(fast > 0) || !(slow > 0))
+            fail(KIPP_E_CONFIG, "yarn_rotary: theta (not 1), factor, original, fast and slow must be positive");
+        return std::make_unique<FrequencyTable>(yarn_frequencies(rot, theta, factor, original, fast, slow),
+                                                format("yarn/%.17g/%d/%.17g/%.17g/%.17g/%.17g", theta, rot, factor, original, fast, slow),
+                                                yarn_magnitude(factor));
+    });
+    r.add_part_kind("gated_mlp", [](const Json& j, const BuildContext&) -> std::unique_ptr<Part> {
+        return std::make_unique<GatedFeedForward>(j);
+    });
+    r.add_part_kind("hyper_connection_block", [](const Json& j, const BuildContext& ctx) -> std::unique_ptr<Part> {
+        const Registry& reg = Registry::get();
+        const Json* n2 = j.find("post_norm");
+        const Json* ff = j.find("ffn");
+        const bool has_ffn = ff != nullptr && !ff->is_null();
+        if (has_ffn && (n2 == nullptr || n2->is_null())) fail(KIPP_E_CONFIG, "hyper_connection_block: a feed-forward needs its post_norm");
+        return std::make_unique<HyperConnectionBlock>(
+            j, reg.make_as<Norm>(j.get("input_norm"), ctx, "a norm"), reg.make_as<Mixer>(j.get("mixer"), ctx, "a mixer"),
+            has_ffn ? reg.make_as<Norm>(*n2, ctx, "a norm") : nullptr,
+            has_ffn ? reg.make_as<FeedForward>(*ff, ctx, "a feed-forward") : nullptr);
     });
     r.add_part_kind("dense_mlp", [](const Json& j, const BuildContext&) -> std::unique_ptr<Part> {
         return std::make_unique<DenseFeedForward>((int)j.get("hidden_size").as_int(), (int)j.get("intermediate_size").as_int(),
@@ -1323,6 +1602,7 @@ inline void register_builtin_parts() {
         options.head_gate = j.get_bool("head_gate", false);
         options.values_are_keys = j.get_bool("values_are_keys", false);
         options.shared_kv = j.get_bool("shared_kv", false);
+        options.softcap = j.get_double("softcap", 0.0);
         options.names = tensor_names(j, options.names);
         return std::make_unique<AttentionMixer>(
             (int)j.get("hidden_size").as_int(), (int)j.get("num_heads").as_int(), (int)j.get("num_kv_heads").as_int(),

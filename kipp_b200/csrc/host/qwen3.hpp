@@ -229,12 +229,14 @@ inline Json plan(const Json& c) {
 void register_venizen();                 // venizen.hpp
 void register_varunex();                 // varunex.hpp
 void register_zasudra();                 // zasudra.hpp
+void register_zunilorn();                // zunilorn.hpp
 
 inline void register_builtin_architectures() {
     Registry::get().add_architecture("Qwen3ForCausalLM", Architecture{qwen3::normalize, qwen3::plan});
     register_venizen();
     register_varunex();
     register_zasudra();
+    register_zunilorn();
 }
 
 }  // namespace kipp

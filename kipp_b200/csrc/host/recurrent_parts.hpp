@@ -621,7 +621,113 @@ private:
     float *mu_ = nullptr, *w_bias_ = nullptr, *bonus_ = nullptr, *norm_ = nullptr;
 };
 
+// The selective state space layer in its matrix-state form (recurrent.cu, kind 4).  One product makes
+// [z: inner | x: inner | B: groups * state | C: groups * state | dt: heads] with inner = heads * v_dim;
+// x, B and C pass a causal convolution per channel (taps from the tensor's shape or `conv`) with bias
+// and silu; dt = softplus(dt + dt_bias); per head (head h uses group h / (heads / groups)):
+// S_t = exp(-exp(A_log_h) dt) S_(t-1) + dt B_t x_t^T (S is state x v_dim), y_t = S_t^T C_t + D_h x_t;
+// y silu(z), divided by the root mean square in norm_groups equal parts of the row, times a weight; then
+// the output projection.  Per request slot: S in float32 and the last taps - 1 inputs of every convolved
+// channel.  Everything behind the projection is float32.
+class StateSpaceMixer : public Mixer {
+public:
+    StateSpaceMixer(const Json& j, const BuildContext&) {
+        hidden_ = (int)j.get("hidden_size").as_int();
+        heads_ = (int)j.get("num_heads").as_int();
+        v_dim_ = (int)j.get("value_dim").as_int();
+        state_ = (int)j.get("state_dim").as_int();
+        groups_ = (int)j.get_int("groups", 1);
+        taps_ = (int)j.get("conv").as_int();
+        norm_groups_ = (int)j.get_int("norm_groups", 1);
+        eps_ = (float)j.get("eps").as_double();
+        names_ = tensor_names(j, {{"in", "in"}, {"conv", "conv"}, {"conv_bias", "conv.b"}, {"dt_bias", "dt_bias"},
+                                  {"a_log", "A_log"}, {"d", "D"}, {"norm", "norm"}, {"o", "o"}});
+        if (hidden_ <= 0 || heads_ <= 0 || v_dim_ <= 0 || state_ <= 0 || groups_ <= 0 || taps_ <= 0 || norm_groups_ <= 0)
+            fail(KIPP_E_CONFIG, "state_space: sizes must be positive");
+        if (heads_ % groups_) fail(KIPP_E_CONFIG, "state_space: num_heads must be a multiple of groups");
+        inner_ = heads_ * v_dim_;
+        if (inner_ % norm_groups_) fail(KIPP_E_CONFIG, "state_space: norm_groups must divide num_heads * value_dim");
+        channels_ = inner_ + 2 * groups_ * state_;
+        proj_cols_ = inner_ + channels_ + heads_;
+        proj_ld_ = (proj_cols_ + 7) / 8 * 8;
+        inner_ld_ = (inner_ + 7) / 8 * 8;
+    }
+    void tensor_specs(const std::string& p, std::vector<TensorSpec>& out) const override {
+        auto add = [&](const char* role, std::vector<int64_t> shape, const char* init = "normal") {
+            TensorSpec s;
+            s.name = p + names_.at(role);
+            s.shape = std::move(shape);
+            s.init = init;
+            out.push_back(s);
+        };
+        add("in", {proj_cols_, hidden_});
+        add("conv", {channels_, taps_});
+        add("conv_bias", {channels_});
+        add("dt_bias", {heads_});
+        add("a_log", {heads_});
+        add("d", {heads_});
+        add("norm", {inner_}, "near_one");
+        add("o", {hidden_, inner_});
+    }
+    long long state_floats() const { return (long long)heads_ * state_ * v_dim_ + (long long)(taps_ - 1) * channels_; }
+    std::optional<StateSpec> state_spec() const override { return StateSpec{{state_floats()}, F32}; }
+    void bind(Binder& b, const std::string& p) override {
+        dtype_ = b.compute_dtype();
+        const size_t es = dtype_size(dtype_);
+        w_in_ = b.allocate((size_t)proj_cols_ * hidden_ * es, p + names_.at("in"));
+        b.load(p + names_.at("in"), w_in_, dtype_, hidden_, proj_cols_, hidden_);
+        w_o_ = b.allocate((size_t)hidden_ * inner_ld_ * es, p + names_.at("o"));
+        cuda_check(cudaMemset(w_o_, 0, (size_t)hidden_ * inner_ld_ * es), "clearing a padded weight");
+        b.load(p + names_.at("o"), w_o_, dtype_, inner_ld_, hidden_, inner_);
+        conv_ = load_f32(b, p + names_.at("conv"), (int64_t)channels_ * taps_);
+        conv_b_ = load_f32(b, p + names_.at("conv_bias"), channels_);
+        dt_bias_ = load_f32(b, p + names_.at("dt_bias"), heads_);
+        a_log_ = load_f32(b, p + names_.at("a_log"), heads_);
+        d_ = load_f32(b, p + names_.at("d"), heads_);
+        norm_ = load_f32(b, p + names_.at("norm"), inner_);
+        if (!Ops::ssd_ok(state_, v_dim_))
+            fail(KIPP_E_UNSUPPORTED, format("state_space: the scan kernel does not take a state of %d x %d", state_, v_dim_));
+        if (Ops::ssd_state_floats(heads_, groups_, state_, v_dim_, taps_) != state_floats())
+            fail(KIPP_E_STATE, "state_space: the kernel library lays the slot out otherwise");
+    }
+    size_t weight_bytes() const override {
+        return ((size_t)proj_cols_ * hidden_ + (size_t)hidden_ * inner_) * dtype_size(dtype_) +
+               ((size_t)channels_ * (taps_ + 1) + 3 * (size_t)heads_ + inner_) * 4;
+    }
+    bool folds_rms() const override { return Ops::gemm_scale_ok(dtype_, w_in_, hidden_, w_in_, hidden_); }
+    void forward(StepContext& ctx, const LayerRun& run, int mixer_slot, const void* h, float* residual) override {
+        const int T = ctx.tokens();
+        const size_t es = ctx.element();
+        Ops& ops = *ctx.ops;
+        const StepMeta& m = *ctx.meta;
+        NormFold fold_in, fold_out;
+        float* state = static_cast<float*>(ctx.state_view(run, mixer_slot, nullptr));
+        void* proj = ctx.workspace->buffer("state_space_proj", (size_t)T * proj_ld_ * es);
+        ops.gemm(proj, ctx.dtype, proj_ld_, h, hidden_, w_in_, hidden_, dtype_, T, proj_cols_, hidden_, EPI_STORE,
+                 fold_input(ctx, fold_in));
+        void* gated = ctx.workspace->buffer("state_space_out", (size_t)T * inner_ld_ * es);
+        if (inner_ld_ != inner_) cuda_check(cudaMemsetAsync(gated, 0, (size_t)T * inner_ld_ * es, ctx.stream), "clearing the padding");
+        ops.ssd_scan(gated, inner_ld_, proj, proj_ld_, ctx.dtype, 0, inner_, inner_ + channels_, conv_, conv_b_, taps_, dt_bias_,
+                     a_log_, d_, norm_, norm_groups_, state, state_floats(), m.q_start, m.entry_of_token, m.slots,
+                     m.shape.entries, T, heads_, groups_, state_, v_dim_, eps_);
+        const NormFold* emit = fold_emit(ctx, fold_out, hidden_);
+        ops.gemm(residual, F32, hidden_, gated, inner_ld_, w_o_, inner_ld_, dtype_, T, hidden_, inner_ld_, EPI_ADD, emit);
+        fold_emitted(ctx, emit, hidden_);
+    }
+
+private:
+    int hidden_ = 0, heads_ = 0, v_dim_ = 0, state_ = 0, groups_ = 1, taps_ = 1, norm_groups_ = 1, inner_ = 0, channels_ = 0,
+        proj_cols_ = 0, proj_ld_ = 0, inner_ld_ = 0, dtype_ = BF16;
+    float eps_ = 0.f;
+    std::map<std::string, std::string> names_;
+    void *w_in_ = nullptr, *w_o_ = nullptr;
+    float *conv_ = nullptr, *conv_b_ = nullptr, *dt_bias_ = nullptr, *a_log_ = nullptr, *d_ = nullptr, *norm_ = nullptr;
+};
+
 inline void register_recurrent_parts(Registry& r) {
+    r.add_part_kind("state_space", [](const Json& j, const BuildContext& ctx) -> std::unique_ptr<Part> {
+        return std::make_unique<StateSpaceMixer>(j, ctx);
+    });
     r.add_part_kind("wkv", [](const Json& j, const BuildContext& ctx) -> std::unique_ptr<Part> {
         return std::make_unique<WkvMixer>(j, ctx);
     });

@@ -10,6 +10,12 @@
 //             times the expert's down projection into one float32 row per pair;
 //   combine   y[t] += sum over the token's choices, in the order of their rank, of weight x row.
 //
+// A second way of routing (kipp_moe_route_scores): scores s = softmax(z) over ALL outputs of the
+// router; the choice by s + correction (a learned number per output that steers the choice only); the
+// weights are the chosen scores divided by their sum, times a scale.  The last outputs of the router
+// may be identity experts, which hand the token's input on: their pairs carry a negative expert id,
+// the lists and products leave them out, and the combine adds weight x input for them.
+//
 // In bfloat16 (sizes that are multiples of 8) the two products take another road: the pairs' input
 // rows are copied into a buffer sorted by expert in which every expert's rows are padded to whole
 // tiles (padded lists, gather), and each projection is ONE grouped product on the tcgen05 kernels
@@ -46,8 +52,8 @@ template <typename T, int TOK>
 __global__ void __launch_bounds__(512)
 moe_route_kernel(int* __restrict__ expert_of, float* __restrict__ weight_of, const T* __restrict__ h, long long ldh,
                  const float* __restrict__ router, const float* __restrict__ bias, int tokens, int hidden, int experts,
-                 int top, int vec) {
-    extern __shared__ float z_all[];                      // [TOK][experts]
+                 int top, int vec, int by_scores, int real_experts, float weight_scale) {
+    extern __shared__ float z_all[];                      // [TOK][experts], and [TOK][experts] scores when by_scores
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
@@ -84,7 +90,7 @@ moe_route_kernel(int* __restrict__ expert_of, float* __restrict__ weight_of, con
 #pragma unroll
         for (int j = 0; j < TOK; ++j) {
             const float sum = warp_sum(acc[j]);
-            if (lane == 0) z_all[(size_t)j * experts + e] = sum + (bias ? bias[e] : 0.f);
+            if (lane == 0) z_all[(size_t)j * experts + e] = sum + (bias && !by_scores ? bias[e] : 0.f);
         }
     }
     __syncthreads();
@@ -92,6 +98,27 @@ moe_route_kernel(int* __restrict__ expert_of, float* __restrict__ weight_of, con
         const int t = t0 + j;
         if (t >= tokens) continue;
         float* z = z_all + (size_t)j * experts;
+        float* score = z_all + (size_t)(TOK + j) * experts;
+        if (by_scores) {
+            // s = softmax(z) over all outputs; what is compared is s + correction
+            float top_z = -INFINITY;
+            for (int e = lane; e < experts; e += 32) top_z = fmaxf(top_z, z[e]);
+            top_z = warp_max(top_z);
+            float sum = 0.f;
+            for (int e = lane; e < experts; e += 32) {
+                const float w = expf(z[e] - top_z);
+                score[e] = w;
+                sum += w;
+            }
+            sum = warp_sum(sum);
+            const float inv = 1.0f / sum;
+            for (int e = lane; e < experts; e += 32) {
+                const float sc = score[e] * inv;
+                score[e] = sc;
+                z[e] = sc + (bias ? bias[e] : 0.f);
+            }
+            __syncwarp();
+        }
         for (int k = 0; k < top; ++k) {
             float best = -INFINITY;
             int idx = INT_MAX;
@@ -107,13 +134,20 @@ moe_route_kernel(int* __restrict__ expert_of, float* __restrict__ weight_of, con
             }
             if (idx >= experts) { idx = k; best = 0.f; }      // logits that are no numbers: still a valid expert
             if (lane == 0) {
-                expert_of[(size_t)t * top + k] = idx;
-                weight_of[(size_t)t * top + k] = best;
+                // an identity expert (an output behind the real experts) is marked by a negative id
+                expert_of[(size_t)t * top + k] = idx < real_experts ? idx : -1 - (idx - real_experts);
+                weight_of[(size_t)t * top + k] = by_scores ? score[idx] : best;
                 z[idx] = -INFINITY;
             }
             __syncwarp();
         }
-        if (lane == 0) {
+        if (lane == 0 && by_scores) {
+            float* w = weight_of + (size_t)t * top;
+            float sum = 0.f;
+            for (int k = 0; k < top; ++k) sum += w[k];
+            const float f = weight_scale / (sum + 1e-20f);
+            for (int k = 0; k < top; ++k) w[k] *= f;
+        } else if (lane == 0) {
             float* w = weight_of + (size_t)t * top;
             const float m = w[0];                            // the largest of the chosen
             float sum = 0.f;
@@ -135,7 +169,8 @@ moe_lists_kernel(int* __restrict__ sorted_pair, int* __restrict__ tile_info, int
     pdl_wait();
     for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
     __syncthreads();
-    for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&counts[expert_of[p]], 1);
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x)
+        if (expert_of[p] >= 0) atomicAdd(&counts[expert_of[p]], 1);      // (a negative id: a pair without an expert's product)
     __syncthreads();
     if (threadIdx.x == 0) {
         int off = 0, nt = 0;
@@ -153,7 +188,8 @@ moe_lists_kernel(int* __restrict__ sorted_pair, int* __restrict__ tile_info, int
     }
     __syncthreads();
     // a pair's place among its expert's rows is whatever the race gives: its row's value does not depend on it
-    for (int p = threadIdx.x; p < pairs; p += blockDim.x) sorted_pair[atomicAdd(&cursor[expert_of[p]], 1)] = p;
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x)
+        if (expert_of[p] >= 0) sorted_pair[atomicAdd(&cursor[expert_of[p]], 1)] = p;
 }
 
 // The pairs sorted by expert with every expert's rows padded to whole tiles of `tile_rows`:
@@ -168,7 +204,8 @@ moe_padded_lists_kernel(int* __restrict__ place_of_pair, int* __restrict__ exper
     pdl_wait();
     for (int e = threadIdx.x; e < experts; e += blockDim.x) counts[e] = 0;
     __syncthreads();
-    for (int p = threadIdx.x; p < pairs; p += blockDim.x) atomicAdd(&counts[expert_of[p]], 1);
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x)
+        if (expert_of[p] >= 0) atomicAdd(&counts[expert_of[p]], 1);
     __syncthreads();
     if (threadIdx.x == 0) {
         int nt = 0;
@@ -180,7 +217,8 @@ moe_padded_lists_kernel(int* __restrict__ place_of_pair, int* __restrict__ exper
     }
     __syncthreads();
     // a pair's place among its expert's rows is whatever the race gives: its row's value does not depend on it
-    for (int p = threadIdx.x; p < pairs; p += blockDim.x) place_of_pair[p] = atomicAdd(&cursor[expert_of[p]], 1);
+    for (int p = threadIdx.x; p < pairs; p += blockDim.x)
+        place_of_pair[p] = expert_of[p] >= 0 ? atomicAdd(&cursor[expert_of[p]], 1) : -1;
 }
 
 // dst[place_of_pair[p], :] = src[p / top, :], 16 bytes per thread and step (bfloat16 rows of 8 n elements).
@@ -191,6 +229,7 @@ moe_gather_rows_kernel(uint4* __restrict__ dst, const uint4* __restrict__ src, l
     pdl_wait();
     const int p = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     if (p >= pairs) return;
+    if (place_of_pair[p] < 0) return;                    // a pair without an expert's product
     const uint4* from = src + (size_t)(p / top) * ld_src16;
     uint4* to = dst + (size_t)place_of_pair[p] * row16;
     for (int i = threadIdx.x & 31; i < row16; i += 32) to[i] = from[i];
@@ -284,14 +323,40 @@ moe_combine_kernel(float* __restrict__ y, const float* __restrict__ rows, const 
         y[(size_t)t * hidden + i] += acc;
     }
 }
+
+// The combine where some pairs are identity experts (expert_of < 0): their row is the token's input.
+template <typename T>
+__global__ void __launch_bounds__(128)
+moe_combine_identity_kernel(float* __restrict__ y, const float* __restrict__ rows, const float* __restrict__ weight_of,
+                            const int* __restrict__ expert_of, const T* __restrict__ h, long long ldh, int hidden, int top,
+                            const int* __restrict__ place_of_pair) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int t = blockIdx.x;
+    const float* w = weight_of + (size_t)t * top;
+    const int* ex = expert_of + (size_t)t * top;
+    for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
+        float acc = 0.f;
+        for (int k = 0; k < top; ++k) {
+            if (ex[k] < 0) {
+                acc = fmaf(w[k], to_f32(h[(size_t)t * ldh + i]), acc);
+            } else {
+                const size_t row = place_of_pair ? (size_t)place_of_pair[(size_t)t * top + k] : (size_t)t * top + k;
+                acc = fmaf(w[k], rows[row * hidden + i], acc);
+            }
+        }
+        y[(size_t)t * hidden + i] += acc;
+    }
+}
 }  // namespace
 
 // Tiles a step of `pairs` (token, choice) pairs over `experts` experts can need at most.
 extern "C" int kipp_moe_max_tiles(int pairs, int experts) { return (pairs + BM - 1) / BM + experts; }
 
 // expert_of, weight_of [tokens, top]: the chosen experts in the order of their logits and their weights.
-extern "C" int kipp_moe_route(int* expert_of, float* weight_of, const void* h, long long ldh, int dtype, const float* router,
-                              const float* bias, int tokens, int hidden, int experts, int top, void* stream) {
+static int moe_route_any(int* expert_of, float* weight_of, const void* h, long long ldh, int dtype, const float* router,
+                         const float* bias, int tokens, int hidden, int experts, int top, int by_scores, int real_experts,
+                         float weight_scale, void* stream) {
     if (tokens <= 0) return 0;
     if (hidden <= 0 || experts <= 0 || top <= 0 || top > experts || experts > 2048) return KIPP_ERR_ARG;
     cudaStream_t s = (cudaStream_t)stream;
@@ -301,22 +366,36 @@ extern "C" int kipp_moe_route(int* expert_of, float* weight_of, const void* h, l
     const int tok = tokens >= 256 ? 4 : 1;
     const int warps = tok == 4 ? 8 : (experts >= 16 ? 16 : experts > 8 ? 8 : 4);
     const dim3 grid((unsigned)((tokens + tok - 1) / tok)), block((unsigned)(32 * warps));
-    const size_t smem = (size_t)tok * experts * sizeof(float);
+    const size_t smem = (size_t)(by_scores ? 2 : 1) * tok * experts * sizeof(float);
     if (dtype == KIPP_DT_F32) {
         if (tok == 4)
             return kipp_launch(moe_route_kernel<float, 4>, grid, block, smem, s, 1, expert_of, weight_of, (const float*)h,
-                               ldh, router, bias, tokens, hidden, experts, top, vec);
+                               ldh, router, bias, tokens, hidden, experts, top, vec, by_scores, real_experts, weight_scale);
         return kipp_launch(moe_route_kernel<float, 1>, grid, block, smem, s, 1, expert_of, weight_of, (const float*)h, ldh,
-                           router, bias, tokens, hidden, experts, top, vec);
+                           router, bias, tokens, hidden, experts, top, vec, by_scores, real_experts, weight_scale);
     }
     if (dtype == KIPP_DT_BF16) {
         if (tok == 4)
             return kipp_launch(moe_route_kernel<bf16, 4>, grid, block, smem, s, 1, expert_of, weight_of, (const bf16*)h, ldh,
-                               router, bias, tokens, hidden, experts, top, vec);
+                               router, bias, tokens, hidden, experts, top, vec, by_scores, real_experts, weight_scale);
         return kipp_launch(moe_route_kernel<bf16, 1>, grid, block, smem, s, 1, expert_of, weight_of, (const bf16*)h, ldh,
-                           router, bias, tokens, hidden, experts, top, vec);
+                           router, bias, tokens, hidden, experts, top, vec, by_scores, real_experts, weight_scale);
     }
     return KIPP_ERR_DTYPE;
+}
+extern "C" int kipp_moe_route(int* expert_of, float* weight_of, const void* h, long long ldh, int dtype, const float* router,
+                              const float* bias, int tokens, int hidden, int experts, int top, void* stream) {
+    return moe_route_any(expert_of, weight_of, h, ldh, dtype, router, bias, tokens, hidden, experts, top, 0, experts, 1.f, stream);
+}
+// Routing by scores: s = softmax(W_r h) over `outputs` router rows, the `top` largest of s + correction
+// (correction null: of s), weights s / (sum of the chosen + 1e-20) * weight_scale.  Outputs from
+// `experts` on are identity experts: expert_of holds -1 - (output - experts) for them.
+extern "C" int kipp_moe_route_scores(int* expert_of, float* weight_of, const void* h, long long ldh, int dtype,
+                                     const float* router, const float* correction, int tokens, int hidden, int outputs,
+                                     int experts, int top, float weight_scale, void* stream) {
+    if (experts < 0 || experts > outputs) return KIPP_ERR_ARG;
+    return moe_route_any(expert_of, weight_of, h, ldh, dtype, router, correction, tokens, hidden, outputs, top, 1, experts,
+                         weight_scale, stream);
 }
 
 // sorted_pair [pairs], tile_info [3 x kipp_moe_max_tiles], n_tiles [1]
@@ -358,6 +437,21 @@ extern "C" int kipp_moe_combine(float* y, const float* rows, const float* weight
     if (hidden <= 0 || top <= 0) return KIPP_ERR_ARG;
     return kipp_launch(moe_combine_kernel, dim3((unsigned)tokens), dim3(128), 0, (cudaStream_t)stream, 1, y, rows, weight_of,
                        hidden, top, place_of_pair);
+}
+
+// The same where pairs with expert_of < 0 stand for the token's own input h [tokens, ldh] (`dtype`).
+extern "C" int kipp_moe_combine_identity(float* y, const float* rows, const float* weight_of, const int* expert_of,
+                                         const void* h, long long ldh, int dtype, int tokens, int hidden, int top,
+                                         const int* place_of_pair, void* stream) {
+    if (tokens <= 0) return 0;
+    if (hidden <= 0 || top <= 0 || expert_of == nullptr || h == nullptr) return KIPP_ERR_ARG;
+    if (dtype == KIPP_DT_F32)
+        return kipp_launch(moe_combine_identity_kernel<float>, dim3((unsigned)tokens), dim3(128), 0, (cudaStream_t)stream, 1, y,
+                           rows, weight_of, expert_of, (const float*)h, ldh, hidden, top, place_of_pair);
+    if (dtype == KIPP_DT_BF16)
+        return kipp_launch(moe_combine_identity_kernel<bf16>, dim3((unsigned)tokens), dim3(128), 0, (cudaStream_t)stream, 1, y,
+                           rows, weight_of, expert_of, (const bf16*)h, ldh, hidden, top, place_of_pair);
+    return KIPP_ERR_DTYPE;
 }
 
 // Tiles of `tile_rows` rows that `pairs` pairs over `experts` experts can need at most when every

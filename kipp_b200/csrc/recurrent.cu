@@ -10,6 +10,11 @@
 //   wkv              o_t = (S_{t-1} + diag(u) k_t v_t^T)^T r_t,   S_t = diag(w_t) S_{t-1} + k_t v_t^T
 //                    (the output reads the OLD state; the bonus u counts the current token only;
 //                    w = exp(-exp(w_raw + w_bias)) per head, key channel and token)
+//   state space     S_t = exp(-exp(A_h) dt_t) S_{t-1} + dt_t B_t x_t^T,   y_t = S_t^T C_t + D_h x_t
+//                    (the selective state space recurrence in its dual, matrix-state form: x, B and C
+//                    pass a short causal convolution and silu first; dt = softplus(dt_raw + bias); the
+//                    heads of a group share B and C; then the gate silu(z), a root-mean-square division
+//                    in equal parts of the row, a weight)
 //
 // S is [key dim, value dim].  Retention rotates q and k by the step's (cos, sin)
 // table (pair (i, i + rot/2), the first `rot` dims) and scales k afterwards; its
@@ -69,12 +74,19 @@ struct ScanArgs {
     float gate_cap, q_scale;
     long long slot_stride;                 // floats per slot of `state` (0: heads * dim * v_dim)
     const float* bonus;                    // wkv: u [heads * dim]
+    // state space: columns of z, of the convolved channels [x: heads * v_dim | B: groups * dim | C: groups * dim]
+    // and of dt in proj; the convolution [channels, taps] with its bias; per head dt's bias, A (as its
+    // logarithm) and D; the slot keeps the last taps - 1 inputs of every channel behind S
+    int z_off, xbc_off, dt_off, taps, groups, norm_groups;
+    const float* conv_w; const float* conv_b;
+    const float* dt_bias; const float* a_log; const float* d_skip;
+    const int* entry_of_token;
 };
-enum { RETENTION = 0, DELTA_RULE = 1, GATED_MEMORY = 2, WKV = 3 };
+enum { RETENTION = 0, DELTA_RULE = 1, GATED_MEMORY = 2, WKV = 3, SSD = 4 };
 // vectors per token besides v, extra floats after them, extra value columns
 template <int KIND> struct Rec {
     static constexpr int NV = KIND == DELTA_RULE ? 5 : KIND == WKV ? 3 : 2;     // wkv: r, k, w
-    static constexpr int XG = KIND == GATED_MEMORY || KIND == WKV ? 4 : 0;      // (i, f, 0, 0), or wkv's (sum u k r, 0, 0, 0), after the vectors
+    static constexpr int XG = KIND == GATED_MEMORY || KIND == WKV || KIND == SSD ? 4 : 0;   // (i, f, 0, 0), wkv's (sum u k r, 0, 0, 0) or the state space's (decay, dt, 0, 0), after the vectors
     static constexpr int XV = KIND == GATED_MEMORY ? 4 : 0;     // value columns (1, 0, 0, 0) after v
 };
 __device__ __forceinline__ float log_sigmoid(float x) { return fminf(x, 0.f) - log1pf(expf(-fabsf(x))); }
@@ -260,6 +272,10 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
                 take = expf(gi - m_new);
                 m_run = m_new;
             }
+            if (KIND == SSD) {
+                keep = tvb[tt * nvd + NV * D];          // exp(-exp(A) dt)
+                take = tvb[tt * nvd + NV * D + 1];      // dt
+            }
             const float* tok = tvb + tt * nvd;
             if (DELTA) {
                 if (VEC) {
@@ -281,7 +297,7 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
                 for (int x = P / 2; x > 0; x >>= 1) us += __shfl_xor_sync(0xffffffffu, us, x);
             }
             float o = 0.f;
-            const float tv = take * v;                  // (gated memory: the input gate's weight on this column's value)
+            const float tv = take * v;                  // (gated memory, state space: the input's weight on this column's value)
             if (VEC) {
 #pragma unroll
                 for (int g = 0; g < CHUNK / 4; ++g) {
@@ -296,7 +312,7 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
                         for (int j = 0; j < 4; ++j) {
                             float s;
                             if (DELTA) s = fmaf(kk[j], v, fmaf(-aa[j], us, ww[j] * S[4 * g + j]));
-                            else if (KIND == GATED_MEMORY) s = fmaf(kk[j], tv, keep * S[4 * g + j]);
+                            else if (KIND == GATED_MEMORY || KIND == SSD) s = fmaf(kk[j], tv, keep * S[4 * g + j]);
                             else if (KIND == WKV) s = fmaf(kk[j], v, ww[j] * S[4 * g + j]);
                             else s = fmaf(kk[j], v, decay * S[4 * g + j]);
                             o = fmaf(KIND == WKV ? S[4 * g + j] : s, qq[j], o);      // wkv reads the old state
@@ -310,7 +326,7 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
                     if (p + P * i < D) {
                         float s;
                         if (DELTA) s = fmaf(base[D + P * i], v, fmaf(-base[3 * D + P * i], us, base[2 * D + P * i] * S[i]));
-                        else if (KIND == GATED_MEMORY) s = fmaf(base[D + P * i], tv, keep * S[i]);
+                        else if (KIND == GATED_MEMORY || KIND == SSD) s = fmaf(base[D + P * i], tv, keep * S[i]);
                         else if (KIND == WKV) s = fmaf(base[D + P * i], v, base[2 * D + P * i] * S[i]);
                         else s = fmaf(base[D + P * i], v, decay * S[i]);
                         o = fmaf(KIND == WKV ? S[i] : s, base[P * i], o);
@@ -368,6 +384,107 @@ recurrent_finish_kernel(const ScanArgs a, const float* __restrict__ o_raw, int t
     }
 }
 
+// The state space layer's token vectors.  A warp per (token, head): the causal convolution (taps
+// inputs per channel: the step's own rows, and before the portion's first token the rows the slot
+// keeps, zeros at a sequence's start) with bias and silu for the head's x and its group's B and C;
+// dt = softplus(dt_raw + bias) without a clamp; the record [C, B, (exp(-exp(A) dt), dt, 0, 0), x].
+template <typename T>
+__global__ void __launch_bounds__(128)
+ssd_prepare_kernel(const ScanArgs a, float* __restrict__ vec, int tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long long wg = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (wg >= (long long)tokens * a.heads) return;
+    const int row = (int)(wg / a.heads), h = (int)(wg % a.heads);
+    const int D = a.dim, V = a.v_dim, taps = a.taps;
+    const int inner = a.heads * V, channels = inner + 2 * a.groups * D;
+    const int g = h / (a.heads / a.groups);
+    const int e = a.entry_of_token[row], first = a.q_start[e];
+    const T* proj = static_cast<const T*>(a.proj);
+    const float* kept = a.state + (size_t)a.slots[e] * (size_t)a.slot_stride + (size_t)a.heads * D * V;   // [taps - 1][channels]
+    auto conv = [&](int c) {
+        float acc = a.conv_b[c];
+        for (int j = 0; j < taps; ++j) {
+            const int r = row - (taps - 1 - j);                     // the row that meets tap j
+            const float in = r >= first ? to_f32(proj[(size_t)r * a.ld_proj + a.xbc_off + c])
+                                        : kept[(size_t)(taps - 1 + r - first) * channels + c];
+            acc = fmaf(a.conv_w[(size_t)c * taps + j], in, acc);
+        }
+        return acc / (1.0f + expf(-acc));
+    };
+    const int rec = 2 * D + 4 + V;
+    float* dst = vec + ((size_t)h * tokens + row) * rec;
+    for (int d = lane; d < D; d += 32) {
+        dst[d] = conv(inner + a.groups * D + g * D + d);           // C: what reads the state
+        dst[D + d] = conv(inner + g * D + d);                       // B: what writes it
+    }
+    for (int c = lane; c < V; c += 32) dst[2 * D + 4 + c] = conv(h * V + c);
+    if (lane == 0) {
+        const float raw = to_f32(proj[(size_t)row * a.ld_proj + a.dt_off + h]) + a.dt_bias[h];
+        const float dt = fmaxf(raw, 0.f) + log1pf(expf(-fabsf(raw)));       // softplus, exact at both ends
+        dst[2 * D] = expf(-expf(a.a_log[h]) * dt);
+        dst[2 * D + 1] = dt;
+        dst[2 * D + 2] = 0.f;
+        dst[2 * D + 3] = 0.f;
+    }
+}
+
+// After the scan: y = (o + D_h x) * silu(z), divided by the root mean square of its part of the row
+// (norm_groups equal parts of heads * v_dim), times the weight.  A warp per (token, part).
+template <typename T>
+__global__ void __launch_bounds__(128)
+ssd_finish_kernel(const ScanArgs a, const float* __restrict__ vec, const float* __restrict__ o_raw, int tokens) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long long wg = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (wg >= (long long)tokens * a.norm_groups) return;
+    const size_t row = (size_t)(wg / a.norm_groups);
+    const int part = (int)(wg % a.norm_groups), V = a.v_dim, inner = a.heads * V, n = inner / a.norm_groups;
+    const int rec = 2 * a.dim + 4 + V;
+    const T* proj = static_cast<const T*>(a.proj) + row * a.ld_proj;
+    auto value = [&](int ch) {
+        const int h = ch / V, c = ch - h * V;
+        const float x = vec[((size_t)h * tokens + row) * rec + 2 * a.dim + 4 + c];
+        const float z = to_f32(proj[a.z_off + ch]);
+        return fmaf(a.d_skip[h], x, o_raw[row * inner + ch]) * (z / (1.0f + expf(-z)));
+    };
+    float ss = 0.f;
+    for (int i = lane; i < n; i += 32) {
+        const float y = value(part * n + i);
+        ss = fmaf(y, y, ss);
+    }
+    ss = warp_sum(ss);
+    const float inv = 1.0f / sqrtf(ss / (float)n + a.eps);
+    T* out = static_cast<T*>(a.out) + row * a.ld_out;
+    for (int i = lane; i < n; i += 32) {
+        const int ch = part * n + i;
+        out[ch] = from_f32<T>(value(ch) * inv * (a.norm_w ? a.norm_w[ch] : 1.f));
+    }
+}
+
+// The slot keeps the last taps - 1 inputs of every convolved channel: the portion's last rows, and
+// where the portion is shorter than that, the rows kept before move up.  A block per entry; a thread
+// walks its channel's rows upward, so that it never overwrites a kept row it still has to read.
+template <typename T>
+__global__ void __launch_bounds__(256)
+ssd_conv_keep_kernel(const ScanArgs a) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int e = blockIdx.x, first = a.q_start[e], n = a.q_start[e + 1] - first, keep = a.taps - 1;
+    if (n <= 0) return;
+    const int channels = a.heads * a.v_dim + 2 * a.groups * a.dim;
+    const T* proj = static_cast<const T*>(a.proj);
+    float* kept = a.state + (size_t)a.slots[e] * (size_t)a.slot_stride + (size_t)a.heads * a.dim * a.v_dim;
+    for (int c = threadIdx.x; c < channels; c += blockDim.x)
+        for (int r = 0; r < keep; ++r) {
+            const int k = n - keep + r;                            // row of the portion, or (negative) a row kept before
+            kept[(size_t)r * channels + c] = k >= 0 ? to_f32(proj[(size_t)(first + k) * a.ld_proj + a.xbc_off + c])
+                                                    : kept[(size_t)(keep + k) * channels + c];
+        }
+}
+
 template <typename T, int DELTA, int P, bool VEC>
 int launch_scan_rows(const ScanArgs& b, const float* vec, float* o_raw, int slices, int tokens, dim3 grid, size_t smem,
                      cudaStream_t stream) {
@@ -406,7 +523,8 @@ int launch_scan(const ScanArgs& a, int entries, int tokens, float* scratch, cuda
     float* o_raw = scratch + (size_t)tokens * a.heads * (NV * D + XG + V);
     const long long warps = (long long)tokens * a.heads;
     const dim3 wgrid((unsigned)((warps + 3) / 4));
-    int rc = kipp_launch(recurrent_prepare_kernel<T, DELTA>, wgrid, dim3(128), 0, stream, 1, b, vec, tokens);
+    int rc = DELTA == SSD ? kipp_launch(ssd_prepare_kernel<T>, wgrid, dim3(128), 0, stream, 1, b, vec, tokens)
+                          : kipp_launch(recurrent_prepare_kernel<T, DELTA>, wgrid, dim3(128), 0, stream, 1, b, vec, tokens);
     if (rc) return rc;
     const int slices = (V + VS - 1) / VS;
     const dim3 grid((unsigned)(entries * a.heads * slices));
@@ -419,6 +537,13 @@ int launch_scan(const ScanArgs& a, int entries, int tokens, float* scratch, cuda
     default: rc = launch_scan_chunk<T, DELTA, 16>(b, vec, o_raw, slices, tokens, grid, smem, stream); break;
     }
     if (rc) return rc;
+    if (DELTA == SSD) {
+        const long long parts = (long long)tokens * b.norm_groups;
+        rc = kipp_launch(ssd_finish_kernel<T>, dim3((unsigned)((parts + 3) / 4)), dim3(128), 0, stream, 1, b, (const float*)vec,
+                         (const float*)o_raw, tokens);
+        if (rc || b.taps <= 1) return rc;
+        return kipp_launch(ssd_conv_keep_kernel<T>, dim3((unsigned)entries), dim3(256), 0, stream, 1, b);
+    }
     return kipp_launch(recurrent_finish_kernel<T, DELTA>, wgrid, dim3(128), 0, stream, 1, b, (const float*)o_raw, tokens);
 }
 
@@ -466,12 +591,12 @@ __global__ void tanh_rows_kernel(T* __restrict__ out, long long ld_out, const T*
 
 // Whether the scan kernels take a head of these sizes.
 extern "C" int kipp_recurrent_scan_ok(int dim, int v_dim, int kind) {
-    if (dim <= 0 || v_dim <= 0 || dim > 16 * MAX_CHUNK || kind < 0 || kind > 3) return 0;
+    if (dim <= 0 || v_dim <= 0 || dim > 16 * MAX_CHUNK || kind < 0 || kind > 4) return 0;
     return (((kind == DELTA_RULE ? 5 : kind == WKV ? 3 : 2) * (size_t)dim + 4 + VS) * sizeof(float)) <= 20 * 1024 ? 1 : 0;
 }
 // float32 values of scratch a scan of `tokens` tokens needs.
 extern "C" long long kipp_recurrent_scratch_floats(int tokens, int heads, int dim, int v_dim, int kind) {
-    const long long x = kind == GATED_MEMORY ? 4 : 0, g = kind == WKV ? 4 : 0;
+    const long long x = kind == GATED_MEMORY ? 4 : 0, g = kind == WKV || kind == SSD ? 4 : 0;
     return (long long)tokens * heads * ((kind == DELTA_RULE ? 5 : kind == WKV ? 3 : 2) * (long long)dim + x + g + 2 * ((long long)v_dim + x));
 }
 // float32 values of state one request slot of the gated memory holds: S with n's column and its
@@ -564,6 +689,39 @@ extern "C" int kipp_wkv_scan(void* out, long long ld_out, const void* proj, long
     a.k_scale = 1.f; a.eps = eps; a.out_scale = out_scale; a.gate = gate;
     if (dtype == KIPP_DT_F32) return launch_scan<float, WKV>(a, entries, tokens, scratch, (cudaStream_t)stream);
     if (dtype == KIPP_DT_BF16) return launch_scan<bf16, WKV>(a, entries, tokens, scratch, (cudaStream_t)stream);
+    return KIPP_ERR_DTYPE;
+}
+
+// float32 values of state one request slot of the state space layer holds: S [heads, dim, v_dim], then the
+// last taps - 1 inputs of the heads * v_dim + 2 * groups * dim convolved channels.
+extern "C" long long kipp_ssd_state_floats(int heads, int groups, int dim, int v_dim, int taps) {
+    return (long long)heads * dim * v_dim + (long long)(taps > 1 ? taps - 1 : 0) * ((long long)heads * v_dim + 2LL * groups * dim);
+}
+
+// The state space layer (see the head of this file).  proj [T, ...] holds z [heads * v_dim] at z_off, the
+// channels to convolve [x | B | C] at xbc_off and dt [heads] at dt_off; conv_w [channels, taps] (the last
+// tap meets the current token), conv_b [channels], dt_bias, a_log, d_skip [heads], norm_w [heads * v_dim]
+// (or null) float32; `dim` is the size of B and C (the state's rows).  A slot is kipp_ssd_state_floats floats.
+extern "C" int kipp_ssd_scan(void* out, long long ld_out, const void* proj, long long ld_proj, int dtype, int z_off,
+                             int xbc_off, int dt_off, const float* conv_w, const float* conv_b, int taps,
+                             const float* dt_bias, const float* a_log, const float* d_skip, const float* norm_w,
+                             int norm_groups, float* state, long long slot_stride, const int* q_start,
+                             const int* entry_of_token, const int* slots, int entries, int tokens, int heads, int groups,
+                             int dim, int v_dim, float eps, float* scratch, void* stream) {
+    if (entries <= 0 || tokens <= 0) return 0;
+    if (!kipp_recurrent_scan_ok(dim, v_dim, SSD) || heads <= 0 || groups <= 0 || heads % groups || taps < 1 ||
+        norm_groups <= 0 || (heads * v_dim) % norm_groups || conv_w == nullptr || conv_b == nullptr || dt_bias == nullptr ||
+        a_log == nullptr || d_skip == nullptr || entry_of_token == nullptr ||
+        slot_stride < kipp_ssd_state_floats(heads, groups, dim, v_dim, taps))
+        return KIPP_ERR_ARG;
+    ScanArgs a = {};
+    a.out = out; a.ld_out = ld_out; a.proj = proj; a.ld_proj = ld_proj;
+    a.z_off = z_off; a.xbc_off = xbc_off; a.dt_off = dt_off; a.taps = taps; a.groups = groups; a.norm_groups = norm_groups;
+    a.conv_w = conv_w; a.conv_b = conv_b; a.dt_bias = dt_bias; a.a_log = a_log; a.d_skip = d_skip; a.norm_w = norm_w;
+    a.state = state; a.slot_stride = slot_stride; a.q_start = q_start; a.entry_of_token = entry_of_token; a.slots = slots;
+    a.heads = heads; a.dim = dim; a.v_dim = v_dim; a.eps = eps; a.k_scale = 1.f; a.out_scale = 1.f;
+    if (dtype == KIPP_DT_F32) return launch_scan<float, SSD>(a, entries, tokens, scratch, (cudaStream_t)stream);
+    if (dtype == KIPP_DT_BF16) return launch_scan<bf16, SSD>(a, entries, tokens, scratch, (cudaStream_t)stream);
     return KIPP_ERR_DTYPE;
 }
 

@@ -328,7 +328,7 @@ int launch_rope_bf16(const void* qkv, int ld_qkv, void* q_out, void* k_pages, vo
 // rotated pair: float32 angle as the reference forms it ((float)position *
 // frequency, src/kipp.c:2374), full-range cosf/sinf.
 __global__ void rope_table_kernel(float2* __restrict__ out, const int* __restrict__ positions,
-                                  const float* __restrict__ inv_freq, int tokens, int half, int by_pair) {
+                                  const float* __restrict__ inv_freq, int tokens, int half, int by_pair, float magnitude) {
     pdl_launch_dependents();
     pdl_wait();
     const int i = blockIdx.x * blockDim.x + threadIdx.x;
@@ -338,7 +338,7 @@ __global__ void rope_table_kernel(float2* __restrict__ out, const int* __restric
     const float angle = (float)positions[t] * inv_freq[k];
     float s, c;
     sincosf(angle, &s, &c);
-    out[i] = make_float2(c, s);
+    out[i] = make_float2(c * magnitude, s * magnitude);
 }
 }  // namespace
 
@@ -348,7 +348,7 @@ extern "C" int kipp_rope_table(void* out, const int* positions, const float* inv
     const long long n = (long long)tokens * half;
     if (n > 0x7fffffffLL) return KIPP_ERR_ARG;
     return kipp_launch(rope_table_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, 1,
-                       (float2*)out, positions, inv_freq, tokens, half, 0);
+                       (float2*)out, positions, inv_freq, tokens, half, 0, 1.0f);
 }
 
 // The same values laid out [half, tokens]: for readers whose neighbouring threads hold
@@ -359,7 +359,18 @@ extern "C" int kipp_rope_table_by_pair(void* out, const int* positions, const fl
     const long long n = (long long)tokens * half;
     if (n > 0x7fffffffLL) return KIPP_ERR_ARG;
     return kipp_launch(rope_table_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, 1,
-                       (float2*)out, positions, inv_freq, tokens, half, 1);
+                       (float2*)out, positions, inv_freq, tokens, half, 1, 1.0f);
+}
+
+// The table with cos and sin both multiplied by `magnitude` (rotations that also stretch the
+// rotated part of q and k); by_pair as above.
+extern "C" int kipp_rope_table_scaled(void* out, const int* positions, const float* inv_freq, int tokens, int half,
+                                      int by_pair, float magnitude, void* stream) {
+    if (tokens <= 0 || half <= 0) return 0;
+    const long long n = (long long)tokens * half;
+    if (n > 0x7fffffffLL) return KIPP_ERR_ARG;
+    return kipp_launch(rope_table_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, 1,
+                       (float2*)out, positions, inv_freq, tokens, half, by_pair ? 1 : 0, magnitude);
 }
 
 // The same with value heads of v_dim elements (in the projection, after the keys, and in the value pages).
