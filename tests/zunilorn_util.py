@@ -92,7 +92,10 @@ INIT = {"A": dict(seed=3, sigma=0.15, norm_jitter=0.2), "B": dict(seed=5, sigma=
 _tmp = tempfile.TemporaryDirectory(prefix="kipp_b200_zunilorn_")
 
 
-def write_folder(folder: str, cfg: dict, init: dict, dtype=torch.float32) -> str:
+def write_folder(folder: str, cfg: dict, init: dict, dtype=torch.bfloat16) -> str:
+    """Weights are stored in bfloat16, as this design's checkpoints are: the 32-bit engine, the
+    16-bit engine (which keeps the small tensors of routers, sinks, decays and connections in
+    float32) and the plain model then all start from the same numbers."""
     from kipp_b200.config import config_from_dict
     from kipp_b200.weights import write_random_model
     return write_random_model(folder, config_from_dict(cfg), init["seed"], sigma=init["sigma"],
