@@ -188,6 +188,26 @@ def zasudra_of(size: str, vocab: int = 32000) -> dict:
             "layers": [order[i % 4] for i in range(layers)]}
 
 
+def zunilorn_of(size: str, vocab: int = 32000) -> dict:
+    """The design's two mixers in turn (the state space layer with heads of 64 over twice the width and
+    a state of 128 rows; attention with a stretched rotation, capped scores, a sink and a gate per
+    head), the first beside a dense gated feed-forward, the others beside sixteen experts of a quarter
+    of the dense width of which a token takes four out of the sixteen and two identity experts, with
+    a shared expert of the same width; four copies of the residual stream."""
+    width, heads, kv, dim, ff, layers = DESIGN_SIZES[size]
+    moe = {"kind": "moe", "expert": {"ff": ff // 4, "limit": 7.0},
+           "router": {"experts": 16, "identity": 2, "top": 4, "scale": 2.5}, "shared": {"ff": ff // 4, "limit": 7.0}}
+    ssm = {"heads": 2 * width // 64, "groups": 8, "vdim": 64, "state": 128, "conv": 4, "norm_groups": 8}
+    att = {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": dim, "scale": dim ** -0.5, "softcap": 50.0,
+           "rot": {"base": 1e6, "dims": dim, "scaling": {"factor": 8.0, "original": 4096, "fast": 32.0, "slow": 1.0}}}
+    order = [{"type": "mamba2", "mixer": ssm, "mlp": {"kind": "dense", "ff": ff, "limit": 7.0}},
+             {"type": "attention", "mixer": att, "mlp": moe},
+             {"type": "mamba2", "mixer": ssm, "mlp": moe},
+             {"type": "attention", "mixer": att, "mlp": moe}]
+    return {"architecture": "Zunilorn", "vocab": vocab, "width": width, "norm": {"eps": 1e-5}, "residual_mult": 0.5,
+            "streams": 4, "logit_softcap": 30.0, "layers": [order[i % 4] for i in range(layers)]}
+
+
 def qwen3_of(size: str, vocab: int = 32000) -> dict:
     width, heads, kv, dim, ff, layers = DESIGN_SIZES[size]
     return dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=vocab, hidden_size=width,
@@ -207,7 +227,8 @@ def compare_designs(args) -> int:
     pk, pk_src = peaks()
     T, B, ctx = args.designs_prompt, args.batch, args.designs_prompt
     families = {"venizen": [("venizen", venizen_of)], "varunex": [("varunex", varunex_of), ("venizen", venizen_of)],
-                "zasudra": [("zasudra", zasudra_of), ("venizen", venizen_of)]}
+                "zasudra": [("zasudra", zasudra_of), ("venizen", venizen_of)],
+                "zunilorn": [("zunilorn", zunilorn_of), ("zasudra", zasudra_of)]}
     designs = families[args.design_family] + [("qwen3", qwen3_of)]
     out = {"metric": "prefill and decode tokens/s, " + " and ".join(d.capitalize() for d, _ in designs[:-1]) +
                      " beside Qwen3 at equal layer sizes", "dtype": "bf16",
@@ -294,9 +315,9 @@ def main() -> int:
                     help="instead of the default workload: a design (--design-family) beside Qwen3 at equal layer sizes, "
                          f"a list of {','.join(DESIGN_SIZES)} (prefill and decode tokens/s, time per kernel)")
     ap.add_argument("--designs-prompt", type=int, default=2048, help="prompt and decode context of --designs")
-    ap.add_argument("--design-family", default="venizen", choices=["venizen", "varunex", "zasudra"],
+    ap.add_argument("--design-family", default="venizen", choices=["venizen", "varunex", "zasudra", "zunilorn"],
                     help="the design --designs measures: venizen, or varunex or zasudra (with Venizen, their closest "
-                         "relative, beside it)")
+                         "relative, beside it), or zunilorn (with Zasudra beside it)")
     args = ap.parse_args()
     if args.impl == "reference":
         return reference_arm(args)

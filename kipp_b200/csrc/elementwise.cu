@@ -576,14 +576,15 @@ extern "C" int kipp_sum_streams(float* out, const float* x, long long stride, in
 // ---------------------------------------------------------------------------------------------
 // A gated feed-forward's activation with limits: g = min(gate + bg, limit), u = clamp(up + bu, -limit, limit),
 // out = g * sigmoid(alpha * g) * (u + 1), in float32 from the projection's stored values.  gate of element i
-// is proj[r, gate_off + i * step], up proj[r, up_off + i * step].  limit <= 0: no limits.  row_gate_col >= 0:
-// the whole row is also multiplied by sigmoid(proj[r, row_gate_col]) (a gate per token on the part's output:
+// is proj[r, gate_off + i * step], up proj[r, up_off + i * step].  limit <= 0: no limits.  row_gate given:
+// the whole row is also multiplied by sigmoid(row_gate[r]) (a gate per token on the part's output:
 // applied here, before the linear down projection).
 namespace {
 template <typename T>
 __global__ void glu_limited_kernel(T* __restrict__ out, long long ld_out, const T* __restrict__ proj, long long ld_proj,
                                    int rows, int n, int gate_off, int up_off, int step, const float* __restrict__ bias_gate,
-                                   const float* __restrict__ bias_up, float limit, float alpha, int row_gate_col) {
+                                   const float* __restrict__ bias_up, int bias_step, float limit, float alpha,
+                                   const float* __restrict__ row_gate) {
     pdl_launch_dependents();
     pdl_wait();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
@@ -592,14 +593,14 @@ __global__ void glu_limited_kernel(T* __restrict__ out, long long ld_out, const 
     const int i = (int)(idx % n);
     const T* pr = proj + r * ld_proj;
     float g = to_f32(pr[gate_off + (long long)i * step]), u = to_f32(pr[up_off + (long long)i * step]);
-    if (bias_gate != nullptr) g += bias_gate[i];
-    if (bias_up != nullptr) u += bias_up[i];
+    if (bias_gate != nullptr) g += bias_gate[(long long)i * bias_step];
+    if (bias_up != nullptr) u += bias_up[(long long)i * bias_step];
     if (limit > 0.f) {
         g = fminf(g, limit);
         u = fminf(fmaxf(u, -limit), limit);
     }
     float v = g / (1.0f + expf(-alpha * g)) * (u + 1.0f);
-    if (row_gate_col >= 0) v *= 1.0f / (1.0f + expf(-to_f32(pr[row_gate_col])));
+    if (row_gate != nullptr) v *= 1.0f / (1.0f + expf(-row_gate[r]));
     out[r * ld_out + i] = from_f32<T>(v);
 }
 
@@ -620,19 +621,48 @@ __global__ void softcap_f32_kernel(float* __restrict__ x, long long n, float cap
 
 extern "C" int kipp_glu_limited(void* out, long long ld_out, const void* proj, long long ld_proj, int dtype, int rows, int n,
                                 int gate_off, int up_off, int step, const float* bias_gate, const float* bias_up,
-                                float limit, float alpha, int row_gate_col, void* stream) {
+                                int bias_step, float limit, float alpha, const float* row_gate, void* stream) {
     if (rows <= 0 || n <= 0) return 0;
     if (step <= 0 || gate_off < 0 || up_off < 0) return KIPP_ERR_ARG;
     const long long total = (long long)rows * n, blocks = (total + 255) / 256;
     if (blocks > 0x7fffffffLL) return KIPP_ERR_ARG;
     if (dtype == KIPP_DT_F32)
         return kipp_launch(glu_limited_kernel<float>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, 1, (float*)out,
-                           ld_out, (const float*)proj, ld_proj, rows, n, gate_off, up_off, step, bias_gate, bias_up, limit,
-                           alpha, row_gate_col);
+                           ld_out, (const float*)proj, ld_proj, rows, n, gate_off, up_off, step, bias_gate, bias_up, bias_step,
+                           limit, alpha, row_gate);
     if (dtype == KIPP_DT_BF16)
         return kipp_launch(glu_limited_kernel<bf16>, dim3((unsigned)blocks), dim3(256), 0, (cudaStream_t)stream, 1, (bf16*)out,
-                           ld_out, (const bf16*)proj, ld_proj, rows, n, gate_off, up_off, step, bias_gate, bias_up, limit,
-                           alpha, row_gate_col);
+                           ld_out, (const bf16*)proj, ld_proj, rows, n, gate_off, up_off, step, bias_gate, bias_up, bias_step,
+                           limit, alpha, row_gate);
+    return KIPP_ERR_DTYPE;
+}
+
+// out[r] = w . h[r, :] in float32 (w float32 [size]; h in `dtype`): a warp per row, the order of the sum
+// fixed by the size.
+namespace {
+template <typename T>
+__global__ void __launch_bounds__(128)
+row_dot_kernel(float* __restrict__ out, const T* __restrict__ h, long long ldh, const float* __restrict__ w, int rows, int size) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int lane = threadIdx.x & 31;
+    const long long r = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
+    if (r >= rows) return;
+    const T* row = h + r * ldh;
+    float acc = 0.f;
+    for (int i = lane; i < size; i += 32) acc = fmaf(w[i], to_f32(row[i]), acc);
+    acc = warp_sum(acc);
+    if (lane == 0) out[r] = acc;
+}
+}  // namespace
+extern "C" int kipp_row_dot(float* out, const void* h, long long ldh, int dtype, const float* w, int rows, int size, void* stream) {
+    if (rows <= 0) return 0;
+    if (size <= 0 || w == nullptr) return KIPP_ERR_ARG;
+    const dim3 grid((unsigned)((rows + 3) / 4));
+    if (dtype == KIPP_DT_F32)
+        return kipp_launch(row_dot_kernel<float>, grid, dim3(128), 0, (cudaStream_t)stream, 1, out, (const float*)h, ldh, w, rows, size);
+    if (dtype == KIPP_DT_BF16)
+        return kipp_launch(row_dot_kernel<bf16>, grid, dim3(128), 0, (cudaStream_t)stream, 1, out, (const bf16*)h, ldh, w, rows, size);
     return KIPP_ERR_DTYPE;
 }
 

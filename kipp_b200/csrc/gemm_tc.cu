@@ -298,7 +298,30 @@ struct Params {
     // Both lie in device memory and may come from the kernel before this one.
     const int* group_of_tile;
     const int* group_tiles;
+    // The gated epilogue (EPI_SWIGLU) in its general form; glu_alpha 0 is the plain silu(gate) * up.
+    // Else: g = min(gate + b, limit), u = clamp(up + b', -limit, limit) (limit 0: none; the biases lie
+    // interleaved like the weight rows, or are null), g sigmoid(alpha g) (u + 1), times
+    // sigmoid(glu_row_gate[token]) where that is given.
+    float glu_alpha, glu_limit;
+    const float* glu_bias;
+    const float* glu_row_gate;
 };
+
+// gate and up of one hidden element (f: the gate's feature index, even) of token t
+__device__ __forceinline__ float glu_of(const Params& p, float g, float u, int f, int t) {
+    if (p.glu_alpha == 0.f) return __fdividef(g, 1.0f + __expf(-g)) * u;
+    if (p.glu_bias != nullptr) {
+        g += p.glu_bias[f];
+        u += p.glu_bias[f + 1];
+    }
+    if (p.glu_limit > 0.f) {
+        g = fminf(g, p.glu_limit);
+        u = fminf(fmaxf(u, -p.glu_limit), p.glu_limit);
+    }
+    float r = g / (1.0f + expf(-p.glu_alpha * g)) * (u + 1.0f);
+    if (p.glu_row_gate != nullptr) r *= 1.0f / (1.0f + expf(-p.glu_row_gate[t]));
+    return r;
+}
 
 // What the next norm needs of a new residual value r of token t, feature f (see Params): called
 // by whole warps whose lanes hold 32 neighbouring features of one token.
@@ -374,7 +397,7 @@ __device__ __forceinline__ void epilogue_chunk(const Params& p, float* v, int t_
             const float u = __shfl_xor_sync(0xffffffffu, v[j], 1);
             const int t = t_first + j;
             if (writer && t < p.tokens) {
-                const float r = __fdividef(v[j], 1.0f + __expf(-v[j])) * u;
+                const float r = glu_of(p, v[j], u, f, t);
                 if (p.out_dtype == KIPP_DT_F32) reinterpret_cast<float*>(p.C)[(size_t)t * p.ldc + (f >> 1)] = r;
                 else reinterpret_cast<bf16*>(p.C)[(size_t)t * p.ldc + (f >> 1)] = __float2bfloat16_rn(r);
             }
@@ -632,7 +655,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant_
                 if (p.epilogue == EPI_SWIGLU) {
                     const float u = __shfl_xor_sync(0xffffffffu, v, 1);
                     if ((lane & 1) == 0 && f + 1 < p.features && t < p.tokens) {
-                        const float r = __fdividef(v, 1.0f + __expf(-v)) * u;
+                        const float r = glu_of(p, v, u, f, t);
                         if (p.out_dtype == KIPP_DT_F32) reinterpret_cast<float*>(p.C)[(size_t)t * p.ldc + (f >> 1)] = r;
                         else reinterpret_cast<bf16*>(p.C)[(size_t)t * p.ldc + (f >> 1)] = __float2bfloat16_rn(r);
                     }
@@ -708,7 +731,7 @@ __device__ __forceinline__ void epilogue_row16(const Params& p, const float* v, 
     } else if (p.epilogue == EPI_SWIGLU) {
         float r[8];
 #pragma unroll
-        for (int i = 0; i < 8; ++i) r[i] = __fdividef(v[2 * i], 1.0f + __expf(-v[2 * i])) * v[2 * i + 1];
+        for (int i = 0; i < 8; ++i) r[i] = f + 2 * i + 1 < p.features ? glu_of(p, v[2 * i], v[2 * i + 1], f + 2 * i, t) : 0.f;
         const size_t at = (size_t)t * p.ldc + (f >> 1);
         if (p.out_dtype == KIPP_DT_F32) {
             float* c = reinterpret_cast<float*>(p.C) + at;
@@ -1581,7 +1604,27 @@ extern "C" int kipp_gemm_tc_fold(void* C, int out_dtype, const void* X, const vo
                        want_tile_f, fold, nullptr, status, stream);
 }
 
+// The general form of the gated epilogue (see Params::glu_alpha): alpha 0 leaves the plain SwiGLU.
+struct kipp_gemm_glu {
+    float alpha, limit;
+    const float* bias;          // [features] float32, interleaved like the weight rows, or null
+    const float* row_gate;      // [tokens] float32: the row is also multiplied by sigmoid of it, or null
+};
+
 namespace {
+// what the entry point of the call in flight asked of the gated epilogue (the launch code below fills
+// Params from it)
+thread_local const kipp_gemm_glu* glu_in_flight = nullptr;
+void apply_glu(Params& p) {
+    if (glu_in_flight == nullptr || p.epilogue != EPI_SWIGLU) return;
+    p.glu_alpha = glu_in_flight->alpha; p.glu_limit = glu_in_flight->limit;
+    p.glu_bias = glu_in_flight->bias; p.glu_row_gate = glu_in_flight->row_gate;
+}
+struct GluScope {
+    explicit GluScope(const kipp_gemm_glu* g) { glu_in_flight = g; }
+    ~GluScope() { glu_in_flight = nullptr; }
+};
+
 int gemm_tc_run(void* C, int out_dtype, const void* X, const void* W, int tokens, int features, int K, long long ldx,
                 long long ldw, long long ldc, int epilogue, int splits, int want_tile, int want_tile_f,
                 const kipp_gemm_norm_fold* fold, const kipp_gemm_head_sink* sink, int* status, void* stream) {
@@ -1656,6 +1699,7 @@ int gemm_tc_run(void* C, int out_dtype, const void* X, const void* W, int tokens
         p.C = C; p.out_dtype = out_dtype; p.epilogue = epilogue;
         p.tokens = tokens; p.features = features; p.K = K; p.ldc = ldc;
         p.k_blocks_per_split = (K + TILE_K - 1) / TILE_K; p.splits = 1; p.status = status;
+        apply_glu(p);
         if (fold != nullptr && fold->ssq_in != nullptr) {
             p.ssq_in = fold->ssq_in; p.ssq_in_slots = fold->ssq_in_slots;
             p.inv_n = fold->inv_n; p.eps = fold->eps;
@@ -1688,6 +1732,7 @@ int gemm_tc_run(void* C, int out_dtype, const void* X, const void* W, int tokens
     const int kb = (K + TILE_K - 1) / TILE_K;
     p.k_blocks_per_split = (kb + splits - 1) / splits;
     p.splits = splits; p.status = status;
+    apply_glu(p);
     if (fold != nullptr) {
         if (fold->norm_w != nullptr) {
             p.norm_w = fold->norm_w; p.norm_w_dtype = fold->norm_w_dtype;
@@ -1732,7 +1777,9 @@ extern "C" int kipp_gemm_tc_grouped(void* C, int out_dtype, const void* X, const
         group_of_tile == nullptr || group_tiles == nullptr)
         return KIPP_ERR_ARG;
     if ((ldx % 8) || (K % 8) || ((uintptr_t)X & 15) || ((uintptr_t)W & 15)) return -3;
-    if ((epilogue & 0xff) != EPI_STORE || (epilogue >> 8) > 4 || epilogue < 0) return KIPP_ERR_ARG;
+    // a store with or without an activation, or the gated epilogue (gate and up rows interleaved in every group)
+    if (epilogue != EPI_SWIGLU && ((epilogue & 0xff) != EPI_STORE || (epilogue >> 8) > 4 || epilogue < 0)) return KIPP_ERR_ARG;
+    if (epilogue == EPI_SWIGLU && (features & 1)) return KIPP_ERR_ARG;
     if (out_dtype != KIPP_DT_F32 && out_dtype != KIPP_DT_BF16) return KIPP_ERR_DTYPE;
     if ((long long)groups * features > 0x7fffffffLL) return KIPP_ERR_ARG;
     if (tile_rows == 16) {
@@ -1746,6 +1793,7 @@ extern "C" int kipp_gemm_tc_grouped(void* C, int out_dtype, const void* X, const
         p.tokens = rows; p.features = features; p.K = K; p.ldc = ldc;
         p.k_blocks_per_split = (K + TILE_K - 1) / TILE_K; p.splits = 1; p.status = status;
         p.group_of_tile = group_of_tile; p.group_tiles = group_tiles;
+        apply_glu(p);
         dim3 grid(rows / 16, (features + 127) / 128, 1);
         if (grid.y > 65535) return KIPP_ERR_ARG;
         return launch<16, 128>(mw, mx, p, grid, (cudaStream_t)stream);
@@ -1761,7 +1809,29 @@ extern "C" int kipp_gemm_tc_grouped(void* C, int out_dtype, const void* X, const
     p.tokens = rows; p.features = features; p.K = K; p.ldc = ldc;
     p.k_blocks_per_split = (K + TILE_K - 1) / TILE_K; p.splits = 1; p.status = status;
     p.group_of_tile = group_of_tile; p.group_tiles = group_tiles;
+    apply_glu(p);
     const long long total = (long long)(rows / UMMA_M) * ((features + tile_n - 1) / tile_n);
     if (total > 0x7fffffffLL) return KIPP_ERR_ARG;
     return launch_tokm_n<false>(tile_n, mw, mx, mw, p, (int)total, (cudaStream_t)stream);
+}
+
+// out[t, i] = glu(gate, up) of the product's neighbouring rows 2i (gate) and 2i + 1 (up): the gated
+// epilogue in its general form (kipp_gemm_glu); `fold` may carry the row factors of a deferred norm.
+extern "C" int kipp_gemm_tc_glu(void* C, int out_dtype, const void* X, const void* W, int tokens, int features, int K,
+                                long long ldx, long long ldw, long long ldc, const kipp_gemm_norm_fold* fold,
+                                const kipp_gemm_glu* glu, int* status, void* stream) {
+    if (glu == nullptr || !(glu->alpha > 0.f) || glu->limit < 0.f) return KIPP_ERR_ARG;
+    GluScope scope(glu);
+    return gemm_tc_run(C, out_dtype, X, W, tokens, features, K, ldx, ldw, ldc, EPI_SWIGLU, 0, 0, 0, fold, nullptr, status, stream);
+}
+// The same for a grouped product (every group's gate and up rows interleaved; no biases).
+extern "C" int kipp_gemm_tc_grouped_glu(void* C, int out_dtype, const void* X, const void* W, int rows, int features, int K,
+                                        long long ldx, long long ldc, int groups, const int* group_of_tile,
+                                        const int* group_tiles, int tile_rows, const kipp_gemm_glu* glu, int* status,
+                                        void* stream) {
+    if (glu == nullptr || !(glu->alpha > 0.f) || glu->limit < 0.f || glu->bias != nullptr || glu->row_gate != nullptr)
+        return KIPP_ERR_ARG;
+    GluScope scope(glu);
+    return kipp_gemm_tc_grouped(C, out_dtype, X, W, rows, features, K, ldx, ldc, groups, EPI_SWIGLU, group_of_tile, group_tiles,
+                                tile_rows, status, stream);
 }

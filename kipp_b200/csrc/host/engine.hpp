@@ -957,6 +957,7 @@ inline const float* Engine::forward(StepMeta& meta) {
         const bool next_plain = i + 1 < plan_->order.size() && !plan_->order[i + 1].adds_embedding;
         ctx.following_norm = next_plain ? plan_->layers[(size_t)plan_->order[i + 1].layer].second->deferred_first_norm()
                                         : nullptr;
+        ctx.following_block = next_plain ? plan_->layers[(size_t)plan_->order[i + 1].layer].second.get() : nullptr;
         plan_->layers[(size_t)run.layer].second->forward(ctx, run, x);
     }
     const float* logits = nullptr;
@@ -1544,6 +1545,7 @@ inline std::string Engine::info_json() {
     counters.set("projections_to_heads", ops_.projections_to_heads);
     counters.set("mix_mma_launches", ops_.mix_mma_launches);
     counters.set("shared_key_launches", ops_.shared_key_launches);
+    counters.set("glu_epilogues", ops_.glu_epilogues);
     j.set("counters", std::move(counters));
     info_ = j.dump();
     return info_;

@@ -80,17 +80,18 @@ public:
         dtype_ = b.compute_dtype();
         const size_t es = dtype_size(dtype_);
         // the experts' matrices one after another, so that a tile finds its expert's by an offset
-        // (a gated expert: its gate's rows, then its up projection's)
+        // (a gated expert: its gate's and its up projection's rows interleaved, gate_0, up_0, gate_1, ...)
         const size_t one = (size_t)inter_ * hidden_, first = (size_t)up_rows_ * hidden_;
         w_up_ = b.allocate((size_t)experts_ * first * es, p + "experts up");
         w_down_ = b.allocate((size_t)experts_ * one * es, p + "experts down");
         for (int e = 0; e < experts_; ++e) {
             char* up = static_cast<char*>(w_up_) + (size_t)e * first * es;
             if (gated_) {
-                b.load(p + expert_name(e, "gate"), up, dtype_, hidden_, inter_, hidden_);
-                up += one * es;
+                b.load(p + expert_name(e, "gate"), up, dtype_, 2 * (int64_t)hidden_, inter_, hidden_);
+                b.load(p + expert_name(e, "up"), up + (size_t)hidden_ * es, dtype_, 2 * (int64_t)hidden_, inter_, hidden_);
+            } else {
+                b.load(p + expert_name(e, "up"), up, dtype_, hidden_, inter_, hidden_);
             }
-            b.load(p + expert_name(e, "up"), up, dtype_, hidden_, inter_, hidden_);
             b.load(p + expert_name(e, "down"), static_cast<char*>(w_down_) + (size_t)e * one * es, dtype_, inter_, hidden_, inter_);
         }
         // the router works in float32
@@ -150,12 +151,12 @@ public:
             route(ctx, expert_of, weight_of, h, T);
             ops.moe_padded_lists(place, tile_expert, n_tiles, expert_of, pairs, experts_, tile);
             ops.moe_gather_rows(in, h, hidden_, place, pairs, top_, hidden_);
-            if (gated_) {
-                void* both = ctx.workspace->buffer("moe_gate_up_rows", (size_t)rows_cap * up_rows_ * ctx.element());
-                ops.gemm_grouped(both, ctx.dtype, up_rows_, in, hidden_, w_up_, rows_cap, up_rows_, hidden_, experts_, -1,
-                                 tile_expert, n_tiles, tile);
-                ops.glu_limited(act, inter_, both, up_rows_, ctx.dtype, rows_cap, inter_, 0, inter_, 1, nullptr, nullptr, limit_,
-                                alpha_, -1);
+            if (gated_) {                           // the gated activation in the grouped product's epilogue
+                Ops::Glu glu;
+                glu.alpha = alpha_;
+                glu.limit = limit_;
+                ops.gemm_grouped_glu(act, ctx.dtype, inter_, in, hidden_, w_up_, rows_cap, up_rows_, hidden_, experts_, glu,
+                                     tile_expert, n_tiles, tile);
             } else {
                 ops.gemm_grouped(act, ctx.dtype, inter_, in, hidden_, w_up_, rows_cap, inter_, hidden_, experts_, act_, tile_expert,
                                  n_tiles, tile);
@@ -181,7 +182,10 @@ public:
             void* both = ctx.workspace->buffer("moe_gate_up", (size_t)pairs * up_rows_ * ctx.element());
             ops.moe_gemm(both, ctx.dtype, up_rows_, h, hidden_, w_up_, (long long)up_rows_ * hidden_, dtype_, up_rows_, hidden_, top_,
                          true, false, -1, sorted, tiles, n_tiles, pairs, experts_);
-            ops.glu_limited(act, inter_, both, up_rows_, ctx.dtype, pairs, inter_, 0, inter_, 1, nullptr, nullptr, limit_, alpha_, -1);
+            Ops::Glu glu;
+            glu.alpha = alpha_;
+            glu.limit = limit_;
+            ops.glu_limited(act, inter_, both, up_rows_, ctx.dtype, pairs, inter_, glu);
         } else
         ops.moe_gemm(act, ctx.dtype, inter_, h, hidden_, w_up_, one, dtype_, inter_, hidden_, top_, true, false, act_, sorted,
                      tiles, n_tiles, pairs, experts_);

@@ -523,18 +523,58 @@ public:
         static Fn f = kernel_symbol<Fn>("elementwise", "kipp_sum_streams");
         run(f(out, x, stride, streams, n, stream), "sum_streams");
     }
-    // out[r, i] = g sigmoid(alpha g) (u + 1), g = min(gate + bg, limit), u = clamp(up + bu, -limit, limit); gate of
-    // element i at proj[r, gate_off + i * step], up at proj[r, up_off + i * step]; row_gate_col >= 0: the row is
-    // also multiplied by sigmoid(proj[r, row_gate_col]).
-    void glu_limited(void* out, long long ld_out, const void* proj, long long ld_proj, int dtype, int rows, int n, int gate_off,
-                     int up_off, int step, const float* bias_gate, const float* bias_up, float limit, float alpha,
-                     int row_gate_col) {
+    // The gated activation with limits, g sigmoid(alpha g) (u + 1) with g = min(gate + b, limit) and
+    // u = clamp(up + b', -limit, limit): `bias` [2 n] float32 interleaved (gate_0, up_0, ...) or null;
+    // row_gate [rows] float32 or null: the row is also multiplied by sigmoid of it.
+    struct Glu {
+        float alpha = 1.f, limit = 0.f;
+        const float* bias = nullptr;
+        const float* row_gate = nullptr;
+    };
+    // out[r, i] = glu(proj[r, 2 i], proj[r, 2 i + 1]): the stored product's neighbouring columns
+    void glu_limited(void* out, long long ld_out, const void* proj, long long ld_proj, int dtype, int rows, int n,
+                     const Glu& glu) {
         using Fn = int (*)(void*, long long, const void*, long long, int, int, int, int, int, int, const float*, const float*,
-                           float, float, int, void*);
+                           int, float, float, const float*, void*);
         static Fn f = kernel_symbol<Fn>("elementwise", "kipp_glu_limited");
-        run(f(out, ld_out, proj, ld_proj, dtype, rows, n, gate_off, up_off, step, bias_gate, bias_up, limit, alpha, row_gate_col,
-              stream),
+        run(f(out, ld_out, proj, ld_proj, dtype, rows, n, 0, 1, 2, glu.bias, glu.bias ? glu.bias + 1 : nullptr, 2, glu.limit,
+              glu.alpha, glu.row_gate, stream),
             "glu_limited");
+    }
+    // out [M, N / 2] = glu of a [M, K] x w [N, K]^T whose rows are interleaved (gate_0, up_0, gate_1, ...):
+    // in the tensor-core product's epilogue where it takes the operands, else a stored product (scratch
+    // [M, ld_scratch]) and the element-wise kernel.
+    void gemm_glu(void* out, int out_dtype, long long ldc, const void* a, long long lda, const void* w, long long ldw, int dtype,
+                  int M, int N, int K, const Glu& glu, const NormFold* fold, void* scratch, long long ld_scratch) {
+        if (M <= 0 || N <= 0) return;
+        if (gemm_tc_ok(dtype, a, lda, w, ldw) && out_dtype == dtype) {
+            using Fn = int (*)(void*, int, const void*, const void*, int, int, int, long long, long long, long long,
+                               const NormFold*, const Glu*, int*, void*);
+            static Fn f = kernel_symbol<Fn>("gemm_tc", "kipp_gemm_tc_glu");
+            run(f(out, out_dtype, a, w, M, N, K, lda, ldw, ldc, fold, &glu, status, stream), "gemm_tc", 1,
+                profiling ? format("gemm_tc %d x %d glu", N, K).c_str() : nullptr);
+            if (fold != nullptr && fold->ssq_in != nullptr) ++folded_norms;
+            ++glu_epilogues;
+            return;
+        }
+        gemm(scratch, dtype, ld_scratch, a, lda, w, ldw, dtype, M, N, K, EPI_STORE, fold);
+        glu_limited(out, ldc, scratch, ld_scratch, dtype, M, N / 2, glu);
+    }
+    // The grouped product (gemm_grouped) with the gated epilogue: every group's rows interleaved.
+    void gemm_grouped_glu(void* out, int out_dtype, long long ldc, const void* a, long long lda, const void* w, int rows, int N,
+                          int K, int groups, const Glu& glu, const int* expert_of_tile, const int* n_tiles, int tile_rows) {
+        using Fn = int (*)(void*, int, const void*, const void*, int, int, int, long long, long long, int, const int*, const int*,
+                           int, const Glu*, int*, void*);
+        static Fn f = kernel_symbol<Fn>("gemm_tc", "kipp_gemm_tc_grouped_glu");
+        run(f(out, out_dtype, a, w, rows, N, K, lda, ldc, groups, expert_of_tile, n_tiles, tile_rows, &glu, status, stream),
+            "gemm_tc_grouped", 1, profiling ? format("gemm_tc_grouped %d x %d glu", N, K).c_str() : nullptr);
+        ++glu_epilogues;
+    }
+    // out[r] = w . h[r, :] in float32
+    void row_dot(float* out, const void* h, long long ldh, int dtype, const float* w, int rows, int size) {
+        using Fn = int (*)(float*, const void*, long long, int, const float*, int, int, void*);
+        static Fn f = kernel_symbol<Fn>("elementwise", "kipp_row_dot");
+        run(f(out, h, ldh, dtype, w, rows, size, stream), "row_dot");
     }
     void add_row_bias(float* x, const float* bias, int rows, int size) {
         using Fn = int (*)(float*, const float*, int, int, void*);
@@ -942,6 +982,7 @@ public:
     long long projections_to_heads = 0;     // q/k/v projections with norm, rotation and cache write inside
     long long mix_mma_launches = 0;         // launches of the tensor-core kernel of the mixed-head attention
     long long shared_key_launches = 0;      // launches of the tensor-core kernel for one shared key row per token
+    long long glu_epilogues = 0;            // gated activations with limits that ran inside a tensor-core product
 };
 
 }  // namespace kipp

@@ -130,6 +130,7 @@ struct RowScale {
 class Engine;
 class Norm;
 class EmbeddingStage;
+class Block;
 
 // What a part sees during one step.
 struct StepContext {
@@ -154,6 +155,11 @@ struct StepContext {
     const Norm* pending_norm = nullptr;    // `normed` holds the deferred form of this norm of the NEXT block
     RowScale pending_scale;
     const Norm* following_norm = nullptr;  // Block::deferred_first_norm of the block that runs next (set by the engine)
+    // The block that runs next on the same stream (set by the engine; null before something else touches
+    // the stream), and the block whose first sublayer's input already lies in `normed`: a block that ends
+    // with a kernel over the whole stream may form the next block's input in that pass and say so here.
+    const Block* following_block = nullptr;
+    const Block* input_ready_for = nullptr;
 
     size_t element() const { return dtype_size(dtype); }
     int tokens() const { return meta->shape.tokens; }

@@ -873,8 +873,10 @@ private:
 // Gated dense feed-forward with limits: g = min(W_gate n + b_g, limit), u = clamp(W_up n + b_u, -limit, limit),
 // x += W_down (g sigmoid(alpha g) (u + 1)) + b_d.  Biases are optional (bias), limit 0 means none.  With
 // row_gate the part's output is also multiplied by sigmoid(w_r . n), one number per token (a tensor
-// [1, hidden]): the factor is applied to the hidden row before the (linear) down projection.  One product
-// makes gate, up and the row gate; the activation runs in float32.
+// [1, hidden], kept in float32): the factor is applied to the hidden row before the (linear) down
+// projection.  Gate and up rows lie interleaved in one matrix, so one product makes both and the
+// activation runs in its epilogue on the float32 sums (tensor-core path), or in a kernel of its own
+// after a stored product (32-bit, odd sizes).
 class GatedFeedForward : public FeedForward {
 public:
     explicit GatedFeedForward(const Json& j) {
@@ -887,10 +889,8 @@ public:
         names_ = tensor_names(j, {{"gate", "gate"}, {"up", "up"}, {"down", "down"}, {"gate_bias", "gate.b"},
                                   {"up_bias", "up.b"}, {"down_bias", "down.b"}, {"row_gate", "sg"}});
         if (hidden_ <= 0 || inter_ <= 0) fail(KIPP_E_CONFIG, "gated_mlp: sizes must be positive");
-        if (limit_ < 0.f) fail(KIPP_E_CONFIG, "gated_mlp: limit must not be negative");
+        if (limit_ < 0.f || !(alpha_ > 0.f)) fail(KIPP_E_CONFIG, "gated_mlp: limit must not be negative and alpha must be positive");
         inter_ld_ = (inter_ + 7) / 8 * 8;
-        proj_cols_ = 2 * inter_ld_ + (row_gate_ ? 1 : 0);        // gate and up each start on a 16-byte boundary of the row
-        proj_ld_ = (proj_cols_ + 7) / 8 * 8;
     }
     void tensor_specs(const std::string& p, std::vector<TensorSpec>& out) const override {
         auto add = [&](const char* role, std::vector<int64_t> shape) {
@@ -912,54 +912,63 @@ public:
     void bind(Binder& b, const std::string& p) override {
         dtype_ = b.compute_dtype();
         const size_t es = dtype_size(dtype_);
-        w_in_ = b.allocate((size_t)proj_cols_ * hidden_ * es, p + "gate, up");
-        cuda_check(cudaMemset(w_in_, 0, (size_t)proj_cols_ * hidden_ * es), "clearing a padded weight");
+        // rows interleaved (gate_0, up_0, gate_1, up_1, ...): a gate sits beside its up value in the epilogue
+        w_in_ = b.allocate((size_t)2 * inter_ * hidden_ * es, p + "gate, up");
         char* base = static_cast<char*>(w_in_);
-        b.load(p + names_.at("gate"), base, dtype_, hidden_, inter_, hidden_);
-        b.load(p + names_.at("up"), base + (size_t)inter_ld_ * hidden_ * es, dtype_, hidden_, inter_, hidden_);
-        if (row_gate_) b.load(p + names_.at("row_gate"), base + (size_t)2 * inter_ld_ * hidden_ * es, dtype_, hidden_, 1, hidden_);
+        b.load(p + names_.at("gate"), base, dtype_, 2 * (int64_t)hidden_, inter_, hidden_);
+        b.load(p + names_.at("up"), base + (size_t)hidden_ * es, dtype_, 2 * (int64_t)hidden_, inter_, hidden_);
         w_down_ = b.allocate((size_t)hidden_ * inter_ld_ * es, p + names_.at("down"));
         cuda_check(cudaMemset(w_down_, 0, (size_t)hidden_ * inter_ld_ * es), "clearing a padded weight");
         b.load(p + names_.at("down"), w_down_, dtype_, inter_ld_, hidden_, inter_);
+        auto floats = [&](const char* role, int64_t n, float* d, int64_t pitch) {
+            if (d == nullptr) d = static_cast<float*>(b.allocate((size_t)n * pitch * sizeof(float), p + names_.at(role)));
+            b.load(p + names_.at(role), d, F32, pitch, n, 1);
+            return d;
+        };
         if (bias_) {
-            auto floats = [&](const char* role, int64_t n) {
-                float* d = static_cast<float*>(b.allocate((size_t)n * sizeof(float), p + names_.at(role)));
-                b.load(p + names_.at(role), d, F32, n, 1, n);
-                return d;
-            };
-            b_gate_ = floats("gate_bias", inter_);
-            b_up_ = floats("up_bias", inter_);
-            b_down_ = floats("down_bias", hidden_);
+            b_in_ = floats("gate_bias", inter_, nullptr, 2);         // interleaved like the rows
+            floats("up_bias", inter_, b_in_ + 1, 2);
+            b_down_ = floats("down_bias", hidden_, nullptr, 1);
         }
+        if (row_gate_) w_row_ = floats("row_gate", hidden_, nullptr, 1);
     }
     size_t weight_bytes() const override {
-        return ((size_t)3 * inter_ + (row_gate_ ? 1 : 0)) * hidden_ * dtype_size(dtype_) + (bias_ ? (size_t)(2 * inter_ + hidden_) * 4 : 0);
+        return (size_t)3 * inter_ * hidden_ * dtype_size(dtype_) + (bias_ ? (size_t)(2 * inter_ + hidden_) * 4 : 0) +
+               (row_gate_ ? (size_t)hidden_ * 4 : 0);
     }
     bool folds_rms() const override { return Ops::gemm_scale_ok(dtype_, w_in_, hidden_, w_in_, hidden_); }
     void forward(StepContext& ctx, const void* h, float* residual) override {
         const int T = ctx.tokens();
         NormFold in, out;
-        void* proj = ctx.workspace->buffer("gated_mlp_proj", (size_t)T * proj_ld_ * ctx.element());
-        ctx.ops->gemm(proj, ctx.dtype, proj_ld_, h, hidden_, w_in_, hidden_, dtype_, T, proj_cols_, hidden_, EPI_STORE,
-                      fold_input(ctx, in));
+        Ops::Glu glu;
+        glu.alpha = alpha_;
+        glu.limit = limit_;
+        glu.bias = b_in_;
+        if (row_gate_) {
+            if (ctx.input_scale.valid()) fail(KIPP_E_STATE, "gated_mlp: a gate per token does not read an input in deferred form");
+            float* logits = ctx.workspace->get<float>("gated_mlp_row_gate", (size_t)T);
+            ctx.ops->row_dot(logits, h, hidden_, ctx.dtype, w_row_, T, hidden_);
+            glu.row_gate = logits;
+        }
         void* act = ctx.workspace->buffer("gated_mlp_act", (size_t)T * inter_ld_ * ctx.element());
         if (inter_ld_ != inter_) cuda_check(cudaMemsetAsync(act, 0, (size_t)T * inter_ld_ * ctx.element(), ctx.stream), "clearing the padding");
-        ctx.ops->glu_limited(act, inter_ld_, proj, proj_ld_, ctx.dtype, T, inter_, 0, inter_ld_, 1, b_gate_, b_up_, limit_, alpha_,
-                             row_gate_ ? 2 * inter_ld_ : -1);
-        const NormFold* emit = fold_emit(ctx, out, hidden_);
+        const bool fused = Ops::gemm_tc_ok(dtype_, h, hidden_, w_in_, hidden_) && ctx.dtype == dtype_;
+        void* proj = fused ? nullptr : ctx.workspace->buffer("gated_mlp_proj", (size_t)T * 2 * inter_ * ctx.element());
+        ctx.ops->gemm_glu(act, ctx.dtype, inter_ld_, h, hidden_, w_in_, hidden_, dtype_, T, 2 * inter_, hidden_, glu,
+                          fold_input(ctx, in), proj, 2 * inter_);
+        const NormFold* emit = b_down_ == nullptr ? fold_emit(ctx, out, hidden_) : nullptr;
         ctx.ops->gemm(residual, F32, hidden_, act, inter_ld_, w_down_, inter_ld_, dtype_, T, hidden_, inter_ld_, EPI_ADD, emit);
-        if (b_down_ != nullptr && emit != nullptr) fail(KIPP_E_STATE, "gated_mlp: a bias on the output does not go with an emitted norm");
         fold_emitted(ctx, emit, hidden_);
         if (b_down_ != nullptr) ctx.ops->add_row_bias(residual, b_down_, T, hidden_);
     }
 
 private:
-    int hidden_ = 0, inter_ = 0, inter_ld_ = 0, proj_cols_ = 0, proj_ld_ = 0, dtype_ = BF16;
+    int hidden_ = 0, inter_ = 0, inter_ld_ = 0, dtype_ = BF16;
     float limit_ = 0.f, alpha_ = 1.f;
     bool bias_ = false, row_gate_ = false;
     std::map<std::string, std::string> names_;
     void *w_in_ = nullptr, *w_down_ = nullptr;
-    float *b_gate_ = nullptr, *b_up_ = nullptr, *b_down_ = nullptr;
+    float *b_in_ = nullptr, *b_down_ = nullptr, *w_row_ = nullptr;
 };
 
 // x += mixer(n) + ffn(n) with n = norm(x): ONE norm whose output both sublayers read.  A block
@@ -1278,19 +1287,37 @@ public:
         auto out_w = [&](int q) { return connections_ ? coef_ + (size_t)q * per + S : nullptr; };
         auto mix = [&](int q) { return connections_ ? coef_ + (size_t)q * per + 2 * S : nullptr; };
         const RmsNormSpec s1 = *n1_->rms_spec();
-        ops.hyper_connection(x, stride, S, nullptr, nullptr, nullptr, 0.f, in_w(0), s1.weight, s1.weight_dtype, s1.eps, h,
-                             ctx.dtype, T, W);
+        // (the block before may have formed this block's first input while it wrote the streams)
+        const bool ready = ctx.input_ready_for == this;
+        ctx.input_ready_for = nullptr;
+        if (!ready)
+            ops.hyper_connection(x, stride, S, nullptr, nullptr, nullptr, 0.f, in_w(0), s1.weight, s1.weight_dtype, s1.eps, h,
+                                 ctx.dtype, T, W);
         cuda_check(cudaMemsetAsync(y, 0, (size_t)T * W * sizeof(float), ctx.stream), "clearing a sublayer's output");
         mixer_->forward(ctx, run, 0, h, y);
+        // the last update of this block also reads the streams for the block that runs next, if that is
+        // one of this kind on as many streams
+        const HyperConnectionBlock* next = dynamic_cast<const HyperConnectionBlock*>(ctx.following_block);
+        if (next != nullptr && (next->streams_ != S || next->n1_->size() != W || !next->n1_->rms_spec())) next = nullptr;
+        auto last_update = [&](int q) {
+            if (next == nullptr) {
+                ops.hyper_connection(x, stride, S, y, mix(q), out_w(q), mult_, nullptr, nullptr, 0, 0.f, nullptr, ctx.dtype, T, W);
+                return;
+            }
+            const RmsNormSpec sn = *next->n1_->rms_spec();
+            ops.hyper_connection(x, stride, S, y, mix(q), out_w(q), mult_, next->connections_ ? next->coef_ : nullptr, sn.weight,
+                                 sn.weight_dtype, sn.eps, h, ctx.dtype, T, W);
+            ctx.input_ready_for = next;
+        };
         if (ffn_) {
             const RmsNormSpec s2 = *n2_->rms_spec();
             ops.hyper_connection(x, stride, S, y, mix(0), out_w(0), mult_, in_w(1), s2.weight, s2.weight_dtype, s2.eps, h,
                                  ctx.dtype, T, W);
             cuda_check(cudaMemsetAsync(y, 0, (size_t)T * W * sizeof(float), ctx.stream), "clearing a sublayer's output");
             ffn_->forward(ctx, h, y);
-            ops.hyper_connection(x, stride, S, y, mix(1), out_w(1), mult_, nullptr, nullptr, 0, 0.f, nullptr, ctx.dtype, T, W);
+            last_update(1);
         } else {
-            ops.hyper_connection(x, stride, S, y, mix(0), out_w(0), mult_, nullptr, nullptr, 0, 0.f, nullptr, ctx.dtype, T, W);
+            last_update(0);
         }
         ctx.emitted = false;
     }

@@ -184,6 +184,13 @@ def test_feed_forward_alone(name, layer, T, dtype):
     out = torch.zeros(T, cfg["width"], device="cuda")
     eng.run_part([StepEntry("f", [0] * T, [])], _run_of(eng, layer), "feed_forward", input=h_dev, residual=out)
     close(out[sure.cuda()], want[sure], dtype, f"{name} layer {layer}")
+    # in bfloat16, sizes that are multiples of 8 run the gated activation inside the products (dense and
+    # shared: one each; the experts: their grouped product); 32-bit and odd sizes use the kernel of its own
+    fused = eng.info()["counters"]["glu_epilogues"]
+    if dtype == "bfloat16" and name in ("A", "C"):
+        assert fused == (1 if mlp["kind"] == "dense" else (2 if mlp.get("shared") else 1))
+    elif dtype == "float32":
+        assert fused == 0
 
 
 def test_the_limits_and_identity_experts_show(tmp_path):
