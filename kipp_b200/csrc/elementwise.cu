@@ -464,10 +464,11 @@ struct HyperArgs {
     int size;
 };
 
-template <typename T>
+// VEC: values per thread and step (4 where the row's size and the pointers allow 16-byte accesses)
+template <typename T, int VEC>
 __global__ void __launch_bounds__(256)
 hyper_connection_kernel(const HyperArgs a) {
-    extern __shared__ float u_row[];                      // [size] when the read phase runs
+    extern __shared__ __align__(16) float u_row[];        // [size] when the read phase runs
     __shared__ float scratch[32];
     __shared__ float c_mix[MAX_STREAMS * MAX_STREAMS], c_out[MAX_STREAMS], c_in[MAX_STREAMS];
     pdl_launch_dependents();
@@ -483,34 +484,49 @@ hyper_connection_kernel(const HyperArgs a) {
     float* row = a.x + (size_t)blockIdx.x * size;
     const float* yr = a.y ? a.y + (size_t)blockIdx.x * size : nullptr;
     float ss = 0.f;
-    for (int i = threadIdx.x; i < size; i += blockDim.x) {
-        float xs[MAX_STREAMS];
+    for (int i = VEC * threadIdx.x; i < size; i += VEC * blockDim.x) {
+        float xs[MAX_STREAMS][VEC];
 #pragma unroll
-        for (int s = 0; s < MAX_STREAMS; ++s)
-            if (s < S) xs[s] = row[(size_t)s * a.stride + i];
+        for (int s = 0; s < MAX_STREAMS; ++s) {
+            if (s >= S) continue;
+            if (VEC == 4) *reinterpret_cast<float4*>(xs[s]) = *reinterpret_cast<const float4*>(row + (size_t)s * a.stride + i);
+            else xs[s][0] = row[(size_t)s * a.stride + i];
+        }
         if (yr != nullptr) {
-            const float y = yr[i];
-            float nx[MAX_STREAMS];
+            float y[VEC], nx[MAX_STREAMS][VEC];
+            if (VEC == 4) *reinterpret_cast<float4*>(y) = *reinterpret_cast<const float4*>(yr + i);
+            else y[0] = yr[i];
 #pragma unroll
             for (int t = 0; t < MAX_STREAMS; ++t) {
                 if (t >= S) continue;
-                float acc = 0.f;
 #pragma unroll
-                for (int s = 0; s < MAX_STREAMS; ++s)
-                    if (s < S) acc = fmaf(c_mix[s * S + t], xs[s], acc);
-                nx[t] = fmaf(c_out[t], y, acc);
+                for (int v = 0; v < VEC; ++v) {
+                    float acc = 0.f;
+#pragma unroll
+                    for (int s = 0; s < MAX_STREAMS; ++s)
+                        if (s < S) acc = fmaf(c_mix[s * S + t], xs[s][v], acc);
+                    nx[t][v] = fmaf(c_out[t], y[v], acc);
+                }
             }
 #pragma unroll
-            for (int t = 0; t < MAX_STREAMS; ++t)
-                if (t < S) { xs[t] = nx[t]; row[(size_t)t * a.stride + i] = nx[t]; }
+            for (int t = 0; t < MAX_STREAMS; ++t) {
+                if (t >= S) continue;
+#pragma unroll
+                for (int v = 0; v < VEC; ++v) xs[t][v] = nx[t][v];
+                if (VEC == 4) *reinterpret_cast<float4*>(row + (size_t)t * a.stride + i) = *reinterpret_cast<const float4*>(nx[t]);
+                else row[(size_t)t * a.stride + i] = nx[t][0];
+            }
         }
         if (read) {
-            float u = 0.f;
 #pragma unroll
-            for (int s = 0; s < MAX_STREAMS; ++s)
-                if (s < S) u = fmaf(c_in[s], xs[s], u);
-            u_row[i] = u;
-            ss = fmaf(u, u, ss);
+            for (int v = 0; v < VEC; ++v) {
+                float u = 0.f;
+#pragma unroll
+                for (int s = 0; s < MAX_STREAMS; ++s)
+                    if (s < S) u = fmaf(c_in[s], xs[s][v], u);
+                u_row[i + v] = u;
+                ss = fmaf(u, u, ss);
+            }
         }
     }
     if (!read) return;
@@ -551,15 +567,14 @@ extern "C" int kipp_hyper_connection(float* x, long long stride, int streams, co
     a.x = x; a.stride = stride; a.S = streams; a.y = y; a.mix = mix; a.out_w = out_w; a.mult = mult;
     a.in_w = in_w; a.norm_w = norm_w; a.norm_w_dtype = norm_w_dtype; a.eps = eps; a.h = h; a.size = size;
     const size_t smem = h != nullptr ? (size_t)size * sizeof(float) : 0;
-    const dim3 grid((unsigned)rows), block(size >= 1024 ? 256 : 128);
-    if (h == nullptr || h_dtype == KIPP_DT_F32) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(hyper_connection_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        return kipp_launch(hyper_connection_kernel<float>, grid, block, smem, (cudaStream_t)stream, 1, a);
-    }
-    if (h_dtype == KIPP_DT_BF16) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(hyper_connection_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        return kipp_launch(hyper_connection_kernel<bf16>, grid, block, smem, (cudaStream_t)stream, 1, a);
-    }
+    const bool vec = size % 4 == 0 && stride % 4 == 0 && (((uintptr_t)x | (uintptr_t)y) & 15) == 0;
+    const dim3 grid((unsigned)rows), block(size >= (vec ? 4096 : 1024) ? 256 : 128);
+    auto go = [&](auto kernel) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        return kipp_launch(kernel, grid, block, smem, (cudaStream_t)stream, 1, a);
+    };
+    if (h == nullptr || h_dtype == KIPP_DT_F32) return vec ? go(hyper_connection_kernel<float, 4>) : go(hyper_connection_kernel<float, 1>);
+    if (h_dtype == KIPP_DT_BF16) return vec ? go(hyper_connection_kernel<bf16, 4>) : go(hyper_connection_kernel<bf16, 1>);
     return KIPP_ERR_DTYPE;
 }
 
@@ -637,28 +652,26 @@ extern "C" int kipp_glu_limited(void* out, long long ld_out, const void* proj, l
     return KIPP_ERR_DTYPE;
 }
 
-// out[r] = w . h[r, :] in float32 (w float32 [size]; h in `dtype`): a warp per row, the order of the sum
+// out[r] = w . h[r, :] in float32 (w float32 [size]; h in `dtype`): a block per row, the order of the sum
 // fixed by the size.
 namespace {
 template <typename T>
 __global__ void __launch_bounds__(128)
 row_dot_kernel(float* __restrict__ out, const T* __restrict__ h, long long ldh, const float* __restrict__ w, int rows, int size) {
+    __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const long long r = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    if (r >= rows) return;
-    const T* row = h + r * ldh;
+    const T* row = h + (size_t)blockIdx.x * ldh;
     float acc = 0.f;
-    for (int i = lane; i < size; i += 32) acc = fmaf(w[i], to_f32(row[i]), acc);
-    acc = warp_sum(acc);
-    if (lane == 0) out[r] = acc;
+    for (int i = threadIdx.x; i < size; i += blockDim.x) acc = fmaf(w[i], to_f32(row[i]), acc);
+    acc = block_sum(acc, scratch);
+    if (threadIdx.x == 0) out[blockIdx.x] = acc;
 }
 }  // namespace
 extern "C" int kipp_row_dot(float* out, const void* h, long long ldh, int dtype, const float* w, int rows, int size, void* stream) {
     if (rows <= 0) return 0;
     if (size <= 0 || w == nullptr) return KIPP_ERR_ARG;
-    const dim3 grid((unsigned)((rows + 3) / 4));
+    const dim3 grid((unsigned)rows);
     if (dtype == KIPP_DT_F32)
         return kipp_launch(row_dot_kernel<float>, grid, dim3(128), 0, (cudaStream_t)stream, 1, out, (const float*)h, ldh, w, rows, size);
     if (dtype == KIPP_DT_BF16)

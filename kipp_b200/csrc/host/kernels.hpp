@@ -637,6 +637,11 @@ public:
         static Fn f = kernel_symbol<Fn>("recurrent", "kipp_recurrent_scan_ok");
         return f(dim, v_dim, 4) != 0;
     }
+    static int ssd_max_taps() {
+        using Fn = int (*)();
+        static Fn f = kernel_symbol<Fn>("recurrent", "kipp_ssd_max_taps");
+        return f();
+    }
     static long long ssd_state_floats(int heads, int groups, int dim, int v_dim, int taps) {
         using Fn = long long (*)(int, int, int, int, int);
         static Fn f = kernel_symbol<Fn>("recurrent", "kipp_ssd_state_floats");
@@ -649,13 +654,14 @@ public:
                   int groups, int dim, int v_dim, float eps) {
         using Fn = int (*)(void*, long long, const void*, long long, int, int, int, int, const float*, const float*, int,
                            const float*, const float*, const float*, const float*, int, float*, long long, const int*,
-                           const int*, const int*, int, int, int, int, int, int, float, float*, void*);
+                           const int*, const int*, int, int, int, int, int, int, float, float*, float*, void*);
         static Fn f = kernel_symbol<Fn>("recurrent", "kipp_ssd_scan");
         float* scratch = recurrent_scratch(tokens, heads, dim, v_dim, 4);
+        float* conv_out = workspace->get<float>("state_space_conv", (size_t)tokens * ((size_t)heads * v_dim + 2 * (size_t)groups * dim));
         run(f(out, ld_out, proj, ld_proj, dtype, z_off, xbc_off, dt_off, conv_w, conv_b, taps, dt_bias, a_log, d_skip, norm_w,
               norm_groups, state, slot_stride, q_start, entry_of_token, slots, entries, tokens, heads, groups, dim, v_dim, eps,
-              scratch, stream),
-            "ssd_scan", taps > 1 ? 4 : 3);
+              scratch, conv_out, stream),
+            "ssd_scan", taps > 1 ? 5 : 4);
     }
 
     // Routing by scores (moe.cu): softmax over all `outputs`, the choice by score + correction, weights

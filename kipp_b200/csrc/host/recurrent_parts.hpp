@@ -687,6 +687,8 @@ public:
         norm_ = load_f32(b, p + names_.at("norm"), inner_);
         if (!Ops::ssd_ok(state_, v_dim_))
             fail(KIPP_E_UNSUPPORTED, format("state_space: the scan kernel does not take a state of %d x %d", state_, v_dim_));
+        if (taps_ > Ops::ssd_max_taps())
+            fail(KIPP_E_UNSUPPORTED, format("state_space: at most %d taps", Ops::ssd_max_taps()));
         if (Ops::ssd_state_floats(heads_, groups_, state_, v_dim_, taps_) != state_floats())
             fail(KIPP_E_STATE, "state_space: the kernel library lays the slot out otherwise");
     }

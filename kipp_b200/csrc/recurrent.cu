@@ -36,6 +36,8 @@
 // Everything that enters the recurrence is formed in float32 from the
 // projections (which arrive in the compute type); the state never leaves float32.
 //
+// (The state space layer's convolution is a kernel of its own before them, and the inputs its slot keeps
+// are written by one after them.)
 // Three kernels per step.  (1) prepare: a warp per (token, head) forms the token's vectors in
 // float32 (q/r, k, and for the delta rule w, a * u, u) in a workspace; fully parallel over the
 // step's tokens.  (2) scan: a block per (entry, head, slice of 32 value columns) -- the columns
@@ -384,42 +386,56 @@ recurrent_finish_kernel(const ScanArgs a, const float* __restrict__ o_raw, int t
     }
 }
 
-// The state space layer's token vectors.  A warp per (token, head): the causal convolution (taps
-// inputs per channel: the step's own rows, and before the portion's first token the rows the slot
-// keeps, zeros at a sequence's start) with bias and silu for the head's x and its group's B and C;
-// dt = softplus(dt_raw + bias) without a clamp; the record [C, B, (exp(-exp(A) dt), dt, 0, 0), x].
+// The state space layer's causal convolution: a thread per (token, channel) sums taps inputs (the
+// step's own rows, and before the portion's first token the rows the slot keeps, zeros at a
+// sequence's start), adds the bias and applies silu; the result stays float32, [tokens, channels].
+constexpr int MAX_TAPS = 16;
+template <typename T>
+__global__ void __launch_bounds__(256)
+ssd_conv_kernel(const ScanArgs a, float* __restrict__ conv_out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int row = blockIdx.x, taps = a.taps;
+    const int channels = a.heads * a.v_dim + 2 * a.groups * a.dim;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (c >= channels) return;
+    const int e = a.entry_of_token[row], first = a.q_start[e];
+    const T* proj = static_cast<const T*>(a.proj);
+    const float* kept = a.state + (size_t)a.slots[e] * (size_t)a.slot_stride + (size_t)a.heads * a.dim * a.v_dim;   // [taps - 1][channels]
+    float acc = a.conv_b[c];
+    for (int j = 0; j < taps; ++j) {
+        const int r = row - (taps - 1 - j);                         // the row that meets tap j
+        const float in = r >= first ? to_f32(proj[(size_t)r * a.ld_proj + a.xbc_off + c])
+                                    : kept[(size_t)(taps - 1 + r - first) * channels + c];
+        acc = fmaf(a.conv_w[(size_t)c * taps + j], in, acc);
+    }
+    conv_out[(size_t)row * channels + c] = acc / (1.0f + expf(-acc));
+}
+
+// The state space layer's token vectors.  A warp per (token, head) copies its group's C and B and its own
+// x out of the convolved row and forms dt = softplus(dt_raw + bias) without a clamp: the record
+// [C, B, (exp(-exp(A) dt), dt, 0, 0), x].
 template <typename T>
 __global__ void __launch_bounds__(128)
-ssd_prepare_kernel(const ScanArgs a, float* __restrict__ vec, int tokens) {
+ssd_prepare_kernel(const ScanArgs a, const float* __restrict__ conv_out, float* __restrict__ vec, int tokens) {
     pdl_launch_dependents();
     pdl_wait();
     const int lane = threadIdx.x & 31;
     const long long wg = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
     if (wg >= (long long)tokens * a.heads) return;
     const int row = (int)(wg / a.heads), h = (int)(wg % a.heads);
-    const int D = a.dim, V = a.v_dim, taps = a.taps;
+    const int D = a.dim, V = a.v_dim;
     const int inner = a.heads * V, channels = inner + 2 * a.groups * D;
     const int g = h / (a.heads / a.groups);
-    const int e = a.entry_of_token[row], first = a.q_start[e];
+    const float* cv = conv_out + (size_t)row * channels;
     const T* proj = static_cast<const T*>(a.proj);
-    const float* kept = a.state + (size_t)a.slots[e] * (size_t)a.slot_stride + (size_t)a.heads * D * V;   // [taps - 1][channels]
-    auto conv = [&](int c) {
-        float acc = a.conv_b[c];
-        for (int j = 0; j < taps; ++j) {
-            const int r = row - (taps - 1 - j);                     // the row that meets tap j
-            const float in = r >= first ? to_f32(proj[(size_t)r * a.ld_proj + a.xbc_off + c])
-                                        : kept[(size_t)(taps - 1 + r - first) * channels + c];
-            acc = fmaf(a.conv_w[(size_t)c * taps + j], in, acc);
-        }
-        return acc / (1.0f + expf(-acc));
-    };
     const int rec = 2 * D + 4 + V;
     float* dst = vec + ((size_t)h * tokens + row) * rec;
     for (int d = lane; d < D; d += 32) {
-        dst[d] = conv(inner + a.groups * D + g * D + d);           // C: what reads the state
-        dst[D + d] = conv(inner + g * D + d);                       // B: what writes it
+        dst[d] = cv[inner + a.groups * D + g * D + d];              // C: what reads the state
+        dst[D + d] = cv[inner + g * D + d];                          // B: what writes it
     }
-    for (int c = lane; c < V; c += 32) dst[2 * D + 4 + c] = conv(h * V + c);
+    for (int c = lane; c < V; c += 32) dst[2 * D + 4 + c] = cv[h * V + c];
     if (lane == 0) {
         const float raw = to_f32(proj[(size_t)row * a.ld_proj + a.dt_off + h]) + a.dt_bias[h];
         const float dt = fmaxf(raw, 0.f) + log1pf(expf(-fabsf(raw)));       // softplus, exact at both ends
@@ -431,58 +447,62 @@ ssd_prepare_kernel(const ScanArgs a, float* __restrict__ vec, int tokens) {
 }
 
 // After the scan: y = (o + D_h x) * silu(z), divided by the root mean square of its part of the row
-// (norm_groups equal parts of heads * v_dim), times the weight.  A warp per (token, part).
+// (norm_groups equal parts of heads * v_dim), times the weight.  A block per (token, part).
 template <typename T>
 __global__ void __launch_bounds__(128)
-ssd_finish_kernel(const ScanArgs a, const float* __restrict__ vec, const float* __restrict__ o_raw, int tokens) {
+ssd_finish_kernel(const ScanArgs a, const float* __restrict__ conv_out, const float* __restrict__ o_raw) {
+    __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
-    const int lane = threadIdx.x & 31;
-    const long long wg = ((long long)blockIdx.x * blockDim.x + threadIdx.x) >> 5;
-    if (wg >= (long long)tokens * a.norm_groups) return;
-    const size_t row = (size_t)(wg / a.norm_groups);
-    const int part = (int)(wg % a.norm_groups), V = a.v_dim, inner = a.heads * V, n = inner / a.norm_groups;
-    const int rec = 2 * a.dim + 4 + V;
+    const size_t row = blockIdx.x / a.norm_groups;
+    const int part = blockIdx.x % a.norm_groups, V = a.v_dim, inner = a.heads * V, n = inner / a.norm_groups;
+    const int channels = inner + 2 * a.groups * a.dim;
     const T* proj = static_cast<const T*>(a.proj) + row * a.ld_proj;
     auto value = [&](int ch) {
-        const int h = ch / V, c = ch - h * V;
-        const float x = vec[((size_t)h * tokens + row) * rec + 2 * a.dim + 4 + c];
+        const float x = conv_out[row * channels + ch];
         const float z = to_f32(proj[a.z_off + ch]);
-        return fmaf(a.d_skip[h], x, o_raw[row * inner + ch]) * (z / (1.0f + expf(-z)));
+        return fmaf(a.d_skip[ch / V], x, o_raw[row * inner + ch]) * (z / (1.0f + expf(-z)));
     };
     float ss = 0.f;
-    for (int i = lane; i < n; i += 32) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const float y = value(part * n + i);
         ss = fmaf(y, y, ss);
     }
-    ss = warp_sum(ss);
+    ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)n + a.eps);
     T* out = static_cast<T*>(a.out) + row * a.ld_out;
-    for (int i = lane; i < n; i += 32) {
+    for (int i = threadIdx.x; i < n; i += blockDim.x) {
         const int ch = part * n + i;
         out[ch] = from_f32<T>(value(ch) * inv * (a.norm_w ? a.norm_w[ch] : 1.f));
     }
 }
 
 // The slot keeps the last taps - 1 inputs of every convolved channel: the portion's last rows, and
-// where the portion is shorter than that, the rows kept before move up.  A block per entry; a thread
-// walks its channel's rows upward, so that it never overwrites a kept row it still has to read.
+// where the portion is shorter than that, the rows kept before move up.  A thread per (entry,
+// channel) reads what it needs first and writes then.
 template <typename T>
 __global__ void __launch_bounds__(256)
 ssd_conv_keep_kernel(const ScanArgs a) {
     pdl_launch_dependents();
     pdl_wait();
     const int e = blockIdx.x, first = a.q_start[e], n = a.q_start[e + 1] - first, keep = a.taps - 1;
-    if (n <= 0) return;
     const int channels = a.heads * a.v_dim + 2 * a.groups * a.dim;
+    const int c = blockIdx.y * blockDim.x + threadIdx.x;
+    if (n <= 0 || c >= channels) return;
     const T* proj = static_cast<const T*>(a.proj);
     float* kept = a.state + (size_t)a.slots[e] * (size_t)a.slot_stride + (size_t)a.heads * a.dim * a.v_dim;
-    for (int c = threadIdx.x; c < channels; c += blockDim.x)
-        for (int r = 0; r < keep; ++r) {
-            const int k = n - keep + r;                            // row of the portion, or (negative) a row kept before
-            kept[(size_t)r * channels + c] = k >= 0 ? to_f32(proj[(size_t)(first + k) * a.ld_proj + a.xbc_off + c])
-                                                    : kept[(size_t)(keep + k) * channels + c];
-        }
+    float rows[MAX_TAPS - 1];
+#pragma unroll
+    for (int r = 0; r < MAX_TAPS - 1; ++r) {
+        if (r >= keep) break;
+        const int k = n - keep + r;                                // row of the portion, or (negative) a row kept before
+        rows[r] = k >= 0 ? to_f32(proj[(size_t)(first + k) * a.ld_proj + a.xbc_off + c]) : kept[(size_t)(keep + k) * channels + c];
+    }
+#pragma unroll
+    for (int r = 0; r < MAX_TAPS - 1; ++r) {
+        if (r >= keep) break;
+        kept[(size_t)r * channels + c] = rows[r];
+    }
 }
 
 template <typename T, int DELTA, int P, bool VEC>
@@ -504,8 +524,9 @@ int launch_scan_chunk(const ScanArgs& b, const float* vec, float* o_raw, int sli
 }
 
 // scratch: float32 [heads][tokens][NV * dim + v_dim] for the records, then [tokens][heads * v_dim] for raw o
+// conv_out: float32 [tokens, channels] for the state space layer's convolved rows (null for the other kinds)
 template <typename T, int DELTA>
-int launch_scan(const ScanArgs& a, int entries, int tokens, float* scratch, cudaStream_t stream) {
+int launch_scan(const ScanArgs& a, int entries, int tokens, float* scratch, cudaStream_t stream, float* conv_out = nullptr) {
     const int D = a.dim, V = a.v_dim + Rec<DELTA>::XV;
     constexpr int NV = Rec<DELTA>::NV, XG = Rec<DELTA>::XG;
     // threads per column: runs of 8 key rows where the head allows (short chains of dependent
@@ -523,8 +544,17 @@ int launch_scan(const ScanArgs& a, int entries, int tokens, float* scratch, cuda
     float* o_raw = scratch + (size_t)tokens * a.heads * (NV * D + XG + V);
     const long long warps = (long long)tokens * a.heads;
     const dim3 wgrid((unsigned)((warps + 3) / 4));
-    int rc = DELTA == SSD ? kipp_launch(ssd_prepare_kernel<T>, wgrid, dim3(128), 0, stream, 1, b, vec, tokens)
-                          : kipp_launch(recurrent_prepare_kernel<T, DELTA>, wgrid, dim3(128), 0, stream, 1, b, vec, tokens);
+    int rc = 0;
+    const int channels = DELTA == SSD ? a.heads * a.v_dim + 2 * a.groups * a.dim : 0;
+    if (DELTA == SSD) {
+        if (conv_out == nullptr) return KIPP_ERR_ARG;
+        rc = kipp_launch(ssd_conv_kernel<T>, dim3((unsigned)tokens, (unsigned)((channels + 255) / 256)), dim3(256), 0, stream, 1, b,
+                         conv_out);
+        if (rc) return rc;
+        rc = kipp_launch(ssd_prepare_kernel<T>, wgrid, dim3(128), 0, stream, 1, b, (const float*)conv_out, vec, tokens);
+    } else {
+        rc = kipp_launch(recurrent_prepare_kernel<T, DELTA>, wgrid, dim3(128), 0, stream, 1, b, vec, tokens);
+    }
     if (rc) return rc;
     const int slices = (V + VS - 1) / VS;
     const dim3 grid((unsigned)(entries * a.heads * slices));
@@ -539,10 +569,13 @@ int launch_scan(const ScanArgs& a, int entries, int tokens, float* scratch, cuda
     if (rc) return rc;
     if (DELTA == SSD) {
         const long long parts = (long long)tokens * b.norm_groups;
-        rc = kipp_launch(ssd_finish_kernel<T>, dim3((unsigned)((parts + 3) / 4)), dim3(128), 0, stream, 1, b, (const float*)vec,
-                         (const float*)o_raw, tokens);
+        if (parts > 0x7fffffffLL) return KIPP_ERR_ARG;
+        const int per_part = a.heads * a.v_dim / b.norm_groups;
+        rc = kipp_launch(ssd_finish_kernel<T>, dim3((unsigned)parts), dim3(per_part >= 128 ? 128 : (per_part + 31) / 32 * 32), 0,
+                         stream, 1, b, (const float*)conv_out, (const float*)o_raw);
         if (rc || b.taps <= 1) return rc;
-        return kipp_launch(ssd_conv_keep_kernel<T>, dim3((unsigned)entries), dim3(256), 0, stream, 1, b);
+        return kipp_launch(ssd_conv_keep_kernel<T>, dim3((unsigned)entries, (unsigned)((channels + 255) / 256)), dim3(256), 0,
+                           stream, 1, b);
     }
     return kipp_launch(recurrent_finish_kernel<T, DELTA>, wgrid, dim3(128), 0, stream, 1, b, (const float*)o_raw, tokens);
 }
@@ -702,14 +735,16 @@ extern "C" long long kipp_ssd_state_floats(int heads, int groups, int dim, int v
 // channels to convolve [x | B | C] at xbc_off and dt [heads] at dt_off; conv_w [channels, taps] (the last
 // tap meets the current token), conv_b [channels], dt_bias, a_log, d_skip [heads], norm_w [heads * v_dim]
 // (or null) float32; `dim` is the size of B and C (the state's rows).  A slot is kipp_ssd_state_floats floats.
+// conv_out: float32 [tokens, channels] of scratch for the convolved rows.  At most 16 taps.
+extern "C" int kipp_ssd_max_taps() { return 16; }
 extern "C" int kipp_ssd_scan(void* out, long long ld_out, const void* proj, long long ld_proj, int dtype, int z_off,
                              int xbc_off, int dt_off, const float* conv_w, const float* conv_b, int taps,
                              const float* dt_bias, const float* a_log, const float* d_skip, const float* norm_w,
                              int norm_groups, float* state, long long slot_stride, const int* q_start,
                              const int* entry_of_token, const int* slots, int entries, int tokens, int heads, int groups,
-                             int dim, int v_dim, float eps, float* scratch, void* stream) {
+                             int dim, int v_dim, float eps, float* scratch, float* conv_out, void* stream) {
     if (entries <= 0 || tokens <= 0) return 0;
-    if (!kipp_recurrent_scan_ok(dim, v_dim, SSD) || heads <= 0 || groups <= 0 || heads % groups || taps < 1 ||
+    if (!kipp_recurrent_scan_ok(dim, v_dim, SSD) || heads <= 0 || groups <= 0 || heads % groups || taps < 1 || taps > MAX_TAPS ||
         norm_groups <= 0 || (heads * v_dim) % norm_groups || conv_w == nullptr || conv_b == nullptr || dt_bias == nullptr ||
         a_log == nullptr || d_skip == nullptr || entry_of_token == nullptr ||
         slot_stride < kipp_ssd_state_floats(heads, groups, dim, v_dim, taps))
@@ -720,8 +755,8 @@ extern "C" int kipp_ssd_scan(void* out, long long ld_out, const void* proj, long
     a.conv_w = conv_w; a.conv_b = conv_b; a.dt_bias = dt_bias; a.a_log = a_log; a.d_skip = d_skip; a.norm_w = norm_w;
     a.state = state; a.slot_stride = slot_stride; a.q_start = q_start; a.entry_of_token = entry_of_token; a.slots = slots;
     a.heads = heads; a.dim = dim; a.v_dim = v_dim; a.eps = eps; a.k_scale = 1.f; a.out_scale = 1.f;
-    if (dtype == KIPP_DT_F32) return launch_scan<float, SSD>(a, entries, tokens, scratch, (cudaStream_t)stream);
-    if (dtype == KIPP_DT_BF16) return launch_scan<bf16, SSD>(a, entries, tokens, scratch, (cudaStream_t)stream);
+    if (dtype == KIPP_DT_F32) return launch_scan<float, SSD>(a, entries, tokens, scratch, (cudaStream_t)stream, conv_out);
+    if (dtype == KIPP_DT_BF16) return launch_scan<bf16, SSD>(a, entries, tokens, scratch, (cudaStream_t)stream, conv_out);
     return KIPP_ERR_DTYPE;
 }
 
