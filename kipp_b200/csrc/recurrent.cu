@@ -52,6 +52,9 @@
 #include <math.h>
 #include <algorithm>
 
+#ifndef KIPP_SSD_WIDE
+#define KIPP_SSD_WIDE 1
+#endif
 namespace {
 constexpr int MAX_CHUNK = 32;
 
@@ -300,7 +303,26 @@ recurrent_scan_kernel(const ScanArgs a, const float* __restrict__ vec, float* __
             }
             float o = 0.f;
             const float tv = take * v;                  // (gated memory, state space: the input's weight on this column's value)
-            if (VEC) {
+            if (VEC && KIND == SSD) {
+                // the state space layer's heads are tall (128 rows and more): a group's four rows are a short chain
+                // of their own, and the groups' sums meet at the end (an order fixed by the sizes)
+                float og[CHUNK / 4];
+#pragma unroll
+                for (int g = 0; g < CHUNK / 4; ++g) {
+                    og[g] = 0.f;
+                    const int r = 4 * (p + P * g);
+                    if (r < D) {
+                        const float4 q4 = *reinterpret_cast<const float4*>(tok + r);
+                        const float4 k4 = *reinterpret_cast<const float4*>(tok + D + r);
+                        const float s0 = fmaf(k4.x, tv, keep * S[4 * g]), s1 = fmaf(k4.y, tv, keep * S[4 * g + 1]);
+                        const float s2 = fmaf(k4.z, tv, keep * S[4 * g + 2]), s3 = fmaf(k4.w, tv, keep * S[4 * g + 3]);
+                        S[4 * g] = s0; S[4 * g + 1] = s1; S[4 * g + 2] = s2; S[4 * g + 3] = s3;
+                        og[g] = fmaf(s3, q4.w, fmaf(s2, q4.z, fmaf(s1, q4.y, s0 * q4.x)));
+                    }
+                }
+#pragma unroll
+                for (int g = 0; g < CHUNK / 4; ++g) o += og[g];
+            } else if (VEC) {
 #pragma unroll
                 for (int g = 0; g < CHUNK / 4; ++g) {
                     const int r = 4 * (p + P * g);
@@ -534,6 +556,7 @@ int launch_scan(const ScanArgs& a, int entries, int tokens, float* scratch, cuda
     int P = 1;
     while (P < 8 && (D + P - 1) / P > 8) P *= 2;
     if ((D + P - 1) / P > MAX_CHUNK) P = 16;
+    if (DELTA == SSD && D > 64 && KIPP_SSD_WIDE) P = 16;
     if ((D + P - 1) / P > MAX_CHUNK || scratch == nullptr) return KIPP_ERR_ARG;
     const size_t per_token = ((size_t)NV * D + XG + VS) * sizeof(float);
     int batch = (int)std::min<size_t>(32, (20 * 1024) / per_token);       // two buffers of at most 20 KB
