@@ -4,6 +4,7 @@
 // token per launch, rms_norm_kernel (cuda/kipp_kernels.cu:44) one row in one
 // block.  These take any number of tokens / rows per launch.
 #include "common.cuh"
+#include <algorithm>
 
 // out[t, :] = float(table[ids[t], :]).  The residual stream is float32.
 template <typename TW>
@@ -457,7 +458,7 @@ namespace {
 constexpr int MAX_STREAMS = 8;
 struct HyperArgs {
     float* x; long long stride; int S;
-    const float* y;
+    float* y; int clear_y;
     const float* mix; const float* out_w; float mult;
     const float* in_w; const void* norm_w; int norm_w_dtype; float eps;
     void* h;
@@ -466,7 +467,7 @@ struct HyperArgs {
 
 // VEC: values per thread and step (4 where the row's size and the pointers allow 16-byte accesses)
 template <typename T, int VEC>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(512)
 hyper_connection_kernel(const HyperArgs a) {
     extern __shared__ __align__(16) float u_row[];        // [size] when the read phase runs
     __shared__ float scratch[32];
@@ -482,7 +483,7 @@ hyper_connection_kernel(const HyperArgs a) {
     __syncthreads();
     const bool read = a.h != nullptr;
     float* row = a.x + (size_t)blockIdx.x * size;
-    const float* yr = a.y ? a.y + (size_t)blockIdx.x * size : nullptr;
+    float* yr = a.y ? a.y + (size_t)blockIdx.x * size : nullptr;
     float ss = 0.f;
     for (int i = VEC * threadIdx.x; i < size; i += VEC * blockDim.x) {
         float xs[MAX_STREAMS][VEC];
@@ -496,6 +497,10 @@ hyper_connection_kernel(const HyperArgs a) {
             float y[VEC], nx[MAX_STREAMS][VEC];
             if (VEC == 4) *reinterpret_cast<float4*>(y) = *reinterpret_cast<const float4*>(yr + i);
             else y[0] = yr[i];
+            if (a.clear_y) {                            // the next sublayer adds its output into zeros
+                if (VEC == 4) *reinterpret_cast<float4*>(yr + i) = make_float4(0.f, 0.f, 0.f, 0.f);
+                else yr[i] = 0.f;
+            }
 #pragma unroll
             for (int t = 0; t < MAX_STREAMS; ++t) {
                 if (t >= S) continue;
@@ -555,7 +560,8 @@ __global__ void sum_streams_kernel(float* __restrict__ out, const float* __restr
 extern "C" int kipp_hyper_connection_max_streams() { return MAX_STREAMS; }
 
 // y null: no update; h null: no read.  mix [S, S] indexed [from, to], out_w [S], in_w [S] float32 (null: identity / ones).
-extern "C" int kipp_hyper_connection(float* x, long long stride, int streams, const float* y, const float* mix,
+// clear_y: y is set to zero once it is read (the buffer the next sublayer adds its output into).
+extern "C" int kipp_hyper_connection(float* x, long long stride, int streams, float* y, int clear_y, const float* mix,
                                      const float* out_w, float mult, const float* in_w, const void* norm_w,
                                      int norm_w_dtype, float eps, void* h, int h_dtype, int rows, int size, void* stream) {
     if (rows <= 0) return 0;
@@ -564,11 +570,16 @@ extern "C" int kipp_hyper_connection(float* x, long long stride, int streams, co
         return KIPP_ERR_ARG;
     if ((size_t)size * sizeof(float) > 160 * 1024) return KIPP_ERR_ARG;
     HyperArgs a;
-    a.x = x; a.stride = stride; a.S = streams; a.y = y; a.mix = mix; a.out_w = out_w; a.mult = mult;
+    a.x = x; a.stride = stride; a.S = streams; a.y = y; a.clear_y = clear_y; a.mix = mix; a.out_w = out_w; a.mult = mult;
     a.in_w = in_w; a.norm_w = norm_w; a.norm_w_dtype = norm_w_dtype; a.eps = eps; a.h = h; a.size = size;
     const size_t smem = h != nullptr ? (size_t)size * sizeof(float) : 0;
     const bool vec = size % 4 == 0 && stride % 4 == 0 && (((uintptr_t)x | (uintptr_t)y) & 15) == 0;
-    const dim3 grid((unsigned)rows), block(size >= (vec ? 4096 : 1024) ? 256 : 128);
+    // a thread's steps wait for one another (loads behind stores to the same row): with few rows as few steps
+    // as the block allows; with rows enough to fill the GPU several times over, small blocks (measured at
+    // 2,048 rows of 4 x 2,048: 36 us with 128 threads, 55 us with 512)
+    const int per = vec ? 4 : 1;
+    const int wide = std::min(512, std::max(64, (size / per + 31) / 32 * 32));
+    const dim3 grid((unsigned)rows), block((unsigned)(rows >= 1024 ? std::min(128, wide) : wide));
     auto go = [&](auto kernel) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         return kipp_launch(kernel, grid, block, smem, (cudaStream_t)stream, 1, a);

@@ -509,13 +509,15 @@ public:
         static Fn f = kernel_symbol<Fn>("elementwise", "kipp_hyper_connection_max_streams");
         return f();
     }
-    void hyper_connection(float* x, long long stride, int streams, const float* y, const float* mix, const float* out_w,
+    // clear_y: y is left zeroed for the sublayer that adds its output into it next.
+    void hyper_connection(float* x, long long stride, int streams, float* y, bool clear_y, const float* mix, const float* out_w,
                           float mult, const float* in_w, const void* norm_w, int norm_w_dtype, float eps, void* h,
                           int h_dtype, int rows, int size) {
-        using Fn = int (*)(float*, long long, int, const float*, const float*, const float*, float, const float*, const void*,
+        using Fn = int (*)(float*, long long, int, float*, int, const float*, const float*, float, const float*, const void*,
                            int, float, void*, int, int, int, void*);
         static Fn f = kernel_symbol<Fn>("elementwise", "kipp_hyper_connection");
-        run(f(x, stride, streams, y, mix, out_w, mult, in_w, norm_w, norm_w_dtype, eps, h, h_dtype, rows, size, stream),
+        run(f(x, stride, streams, y, clear_y ? 1 : 0, mix, out_w, mult, in_w, norm_w, norm_w_dtype, eps, h, h_dtype, rows, size,
+              stream),
             "hyper_connection");
     }
     void sum_streams(float* out, const float* x, long long stride, int streams, long long n) {

@@ -1290,10 +1290,13 @@ public:
         // (the block before may have formed this block's first input while it wrote the streams)
         const bool ready = ctx.input_ready_for == this;
         ctx.input_ready_for = nullptr;
-        if (!ready)
-            ops.hyper_connection(x, stride, S, nullptr, nullptr, nullptr, 0.f, in_w(0), s1.weight, s1.weight_dtype, s1.eps, h,
-                                 ctx.dtype, T, W);
-        cuda_check(cudaMemsetAsync(y, 0, (size_t)T * W * sizeof(float), ctx.stream), "clearing a sublayer's output");
+        // y, the float32 buffer a sublayer adds its output into, is cleared by the kernel that reads it; only a
+        // block that starts on its own (the first of a step) clears it itself
+        if (!ready) {
+            ops.hyper_connection(x, stride, S, nullptr, false, nullptr, nullptr, 0.f, in_w(0), s1.weight, s1.weight_dtype, s1.eps,
+                                 h, ctx.dtype, T, W);
+            cuda_check(cudaMemsetAsync(y, 0, (size_t)T * W * sizeof(float), ctx.stream), "clearing a sublayer's output");
+        }
         mixer_->forward(ctx, run, 0, h, y);
         // the last update of this block also reads the streams for the block that runs next, if that is
         // one of this kind on as many streams
@@ -1301,19 +1304,19 @@ public:
         if (next != nullptr && (next->streams_ != S || next->n1_->size() != W || !next->n1_->rms_spec())) next = nullptr;
         auto last_update = [&](int q) {
             if (next == nullptr) {
-                ops.hyper_connection(x, stride, S, y, mix(q), out_w(q), mult_, nullptr, nullptr, 0, 0.f, nullptr, ctx.dtype, T, W);
+                ops.hyper_connection(x, stride, S, y, false, mix(q), out_w(q), mult_, nullptr, nullptr, 0, 0.f, nullptr, ctx.dtype,
+                                     T, W);
                 return;
             }
             const RmsNormSpec sn = *next->n1_->rms_spec();
-            ops.hyper_connection(x, stride, S, y, mix(q), out_w(q), mult_, next->connections_ ? next->coef_ : nullptr, sn.weight,
-                                 sn.weight_dtype, sn.eps, h, ctx.dtype, T, W);
+            ops.hyper_connection(x, stride, S, y, true, mix(q), out_w(q), mult_, next->connections_ ? next->coef_ : nullptr,
+                                 sn.weight, sn.weight_dtype, sn.eps, h, ctx.dtype, T, W);
             ctx.input_ready_for = next;
         };
         if (ffn_) {
             const RmsNormSpec s2 = *n2_->rms_spec();
-            ops.hyper_connection(x, stride, S, y, mix(0), out_w(0), mult_, in_w(1), s2.weight, s2.weight_dtype, s2.eps, h,
+            ops.hyper_connection(x, stride, S, y, true, mix(0), out_w(0), mult_, in_w(1), s2.weight, s2.weight_dtype, s2.eps, h,
                                  ctx.dtype, T, W);
-            cuda_check(cudaMemsetAsync(y, 0, (size_t)T * W * sizeof(float), ctx.stream), "clearing a sublayer's output");
             ffn_->forward(ctx, h, y);
             last_update(1);
         } else {

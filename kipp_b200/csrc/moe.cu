@@ -307,7 +307,7 @@ moe_gemm_kernel(const GemmArgs g) {
     }
 }
 
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(512)
 moe_combine_kernel(float* __restrict__ y, const float* __restrict__ rows, const float* __restrict__ weight_of, int hidden,
                    int top, const int* __restrict__ place_of_pair) {
     pdl_launch_dependents();
@@ -326,7 +326,7 @@ moe_combine_kernel(float* __restrict__ y, const float* __restrict__ rows, const 
 
 // The combine where some pairs are identity experts (expert_of < 0): their row is the token's input.
 template <typename T>
-__global__ void __launch_bounds__(128)
+__global__ void __launch_bounds__(512)
 moe_combine_identity_kernel(float* __restrict__ y, const float* __restrict__ rows, const float* __restrict__ weight_of,
                             const int* __restrict__ expert_of, const T* __restrict__ h, long long ldh, int hidden, int top,
                             const int* __restrict__ place_of_pair) {
@@ -435,8 +435,9 @@ extern "C" int kipp_moe_combine(float* y, const float* rows, const float* weight
                                 const int* place_of_pair, void* stream) {
     if (tokens <= 0) return 0;
     if (hidden <= 0 || top <= 0) return KIPP_ERR_ARG;
-    return kipp_launch(moe_combine_kernel, dim3((unsigned)tokens), dim3(128), 0, (cudaStream_t)stream, 1, y, rows, weight_of,
-                       hidden, top, place_of_pair);
+    // (an element's steps wait for one another, the loads behind the store before them: few elements per thread)
+    return kipp_launch(moe_combine_kernel, dim3((unsigned)tokens), dim3(hidden >= 2048 ? 512 : hidden >= 512 ? 256 : 128), 0,
+                       (cudaStream_t)stream, 1, y, rows, weight_of, hidden, top, place_of_pair);
 }
 
 // The same where pairs with expert_of < 0 stand for the token's own input h [tokens, ldh] (`dtype`).
@@ -446,10 +447,10 @@ extern "C" int kipp_moe_combine_identity(float* y, const float* rows, const floa
     if (tokens <= 0) return 0;
     if (hidden <= 0 || top <= 0 || expert_of == nullptr || h == nullptr) return KIPP_ERR_ARG;
     if (dtype == KIPP_DT_F32)
-        return kipp_launch(moe_combine_identity_kernel<float>, dim3((unsigned)tokens), dim3(128), 0, (cudaStream_t)stream, 1, y,
+        return kipp_launch(moe_combine_identity_kernel<float>, dim3((unsigned)tokens), dim3(hidden >= 2048 ? 512 : hidden >= 512 ? 256 : 128), 0, (cudaStream_t)stream, 1, y,
                            rows, weight_of, expert_of, (const float*)h, ldh, hidden, top, place_of_pair);
     if (dtype == KIPP_DT_BF16)
-        return kipp_launch(moe_combine_identity_kernel<bf16>, dim3((unsigned)tokens), dim3(128), 0, (cudaStream_t)stream, 1, y,
+        return kipp_launch(moe_combine_identity_kernel<bf16>, dim3((unsigned)tokens), dim3(hidden >= 2048 ? 512 : hidden >= 512 ? 256 : 128), 0, (cudaStream_t)stream, 1, y,
                            rows, weight_of, expert_of, (const bf16*)h, ldh, hidden, top, place_of_pair);
     return KIPP_ERR_DTYPE;
 }
