@@ -465,9 +465,10 @@ struct HyperArgs {
     int size;
 };
 
-// VEC: values per thread and step (4 where the row's size and the pointers allow 16-byte accesses)
-template <typename T, int VEC>
-__global__ void __launch_bounds__(512)
+// VEC: values per thread and step (4 where the row's size and the pointers allow 16-byte accesses); MS: the
+// most copies this instance holds (4 keeps a thread's values in few enough registers for blocks of 512)
+template <typename T, int VEC, int MS>
+__global__ void __launch_bounds__(MS <= 4 ? 512 : 256)
 hyper_connection_kernel(const HyperArgs a) {
     extern __shared__ __align__(16) float u_row[];        // [size] when the read phase runs
     __shared__ float scratch[32];
@@ -486,15 +487,15 @@ hyper_connection_kernel(const HyperArgs a) {
     float* yr = a.y ? a.y + (size_t)blockIdx.x * size : nullptr;
     float ss = 0.f;
     for (int i = VEC * threadIdx.x; i < size; i += VEC * blockDim.x) {
-        float xs[MAX_STREAMS][VEC];
+        float xs[MS][VEC];
 #pragma unroll
-        for (int s = 0; s < MAX_STREAMS; ++s) {
+        for (int s = 0; s < MS; ++s) {
             if (s >= S) continue;
             if (VEC == 4) *reinterpret_cast<float4*>(xs[s]) = *reinterpret_cast<const float4*>(row + (size_t)s * a.stride + i);
             else xs[s][0] = row[(size_t)s * a.stride + i];
         }
         if (yr != nullptr) {
-            float y[VEC], nx[MAX_STREAMS][VEC];
+            float y[VEC], nx[MS][VEC];
             if (VEC == 4) *reinterpret_cast<float4*>(y) = *reinterpret_cast<const float4*>(yr + i);
             else y[0] = yr[i];
             if (a.clear_y) {                            // the next sublayer adds its output into zeros
@@ -502,19 +503,19 @@ hyper_connection_kernel(const HyperArgs a) {
                 else yr[i] = 0.f;
             }
 #pragma unroll
-            for (int t = 0; t < MAX_STREAMS; ++t) {
+            for (int t = 0; t < MS; ++t) {
                 if (t >= S) continue;
 #pragma unroll
                 for (int v = 0; v < VEC; ++v) {
                     float acc = 0.f;
 #pragma unroll
-                    for (int s = 0; s < MAX_STREAMS; ++s)
+                    for (int s = 0; s < MS; ++s)
                         if (s < S) acc = fmaf(c_mix[s * S + t], xs[s][v], acc);
                     nx[t][v] = fmaf(c_out[t], y[v], acc);
                 }
             }
 #pragma unroll
-            for (int t = 0; t < MAX_STREAMS; ++t) {
+            for (int t = 0; t < MS; ++t) {
                 if (t >= S) continue;
 #pragma unroll
                 for (int v = 0; v < VEC; ++v) xs[t][v] = nx[t][v];
@@ -527,7 +528,7 @@ hyper_connection_kernel(const HyperArgs a) {
             for (int v = 0; v < VEC; ++v) {
                 float u = 0.f;
 #pragma unroll
-                for (int s = 0; s < MAX_STREAMS; ++s)
+                for (int s = 0; s < MS; ++s)
                     if (s < S) u = fmaf(c_in[s], xs[s][v], u);
                 u_row[i + v] = u;
                 ss = fmaf(u, u, ss);
@@ -578,14 +579,21 @@ extern "C" int kipp_hyper_connection(float* x, long long stride, int streams, fl
     // as the block allows; with rows enough to fill the GPU several times over, small blocks (measured at
     // 2,048 rows of 4 x 2,048: 36 us with 128 threads, 55 us with 512)
     const int per = vec ? 4 : 1;
-    const int wide = std::min(512, std::max(64, (size / per + 31) / 32 * 32));
+    const int wide = std::min(streams <= 4 ? 512 : 256, std::max(64, (size / per + 31) / 32 * 32));
     const dim3 grid((unsigned)rows), block((unsigned)(rows >= 1024 ? std::min(128, wide) : wide));
     auto go = [&](auto kernel) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         return kipp_launch(kernel, grid, block, smem, (cudaStream_t)stream, 1, a);
     };
-    if (h == nullptr || h_dtype == KIPP_DT_F32) return vec ? go(hyper_connection_kernel<float, 4>) : go(hyper_connection_kernel<float, 1>);
-    if (h_dtype == KIPP_DT_BF16) return vec ? go(hyper_connection_kernel<bf16, 4>) : go(hyper_connection_kernel<bf16, 1>);
+    const bool f32 = h == nullptr || h_dtype == KIPP_DT_F32;
+    if (!f32 && h_dtype != KIPP_DT_BF16) return KIPP_ERR_DTYPE;
+    if (streams <= 4) {
+        if (f32) return vec ? go(hyper_connection_kernel<float, 4, 4>) : go(hyper_connection_kernel<float, 1, 4>);
+        return vec ? go(hyper_connection_kernel<bf16, 4, 4>) : go(hyper_connection_kernel<bf16, 1, 4>);
+    }
+    if (f32) return vec ? go(hyper_connection_kernel<float, 4, MAX_STREAMS>) : go(hyper_connection_kernel<float, 1, MAX_STREAMS>);
+    if (h_dtype == KIPP_DT_BF16)
+        return vec ? go(hyper_connection_kernel<bf16, 4, MAX_STREAMS>) : go(hyper_connection_kernel<bf16, 1, MAX_STREAMS>);
     return KIPP_ERR_DTYPE;
 }
 

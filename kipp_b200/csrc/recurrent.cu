@@ -485,15 +485,29 @@ ssd_finish_kernel(const ScanArgs a, const float* __restrict__ conv_out, const fl
         const float z = to_f32(proj[a.z_off + ch]);
         return fmaf(a.d_skip[ch / V], x, o_raw[row * inner + ch]) * (z / (1.0f + expf(-z)));
     };
+    // a thread's first values stay in registers between the two passes (all of them for parts of up to 1,024)
+    constexpr int HELD = 8;
+    float held[HELD];
     float ss = 0.f;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+#pragma unroll
+    for (int k = 0; k < HELD; ++k) {
+        const int i = threadIdx.x + k * blockDim.x;
+        held[k] = i < n ? value(part * n + i) : 0.f;
+        ss = fmaf(held[k], held[k], ss);
+    }
+    for (int i = threadIdx.x + HELD * blockDim.x; i < n; i += blockDim.x) {
         const float y = value(part * n + i);
         ss = fmaf(y, y, ss);
     }
     ss = block_sum(ss, scratch);
     const float inv = 1.0f / sqrtf(ss / (float)n + a.eps);
     T* out = static_cast<T*>(a.out) + row * a.ld_out;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
+#pragma unroll
+    for (int k = 0; k < HELD; ++k) {
+        const int i = threadIdx.x + k * blockDim.x, ch = part * n + i;
+        if (i < n) out[ch] = from_f32<T>(held[k] * inv * (a.norm_w ? a.norm_w[ch] : 1.f));
+    }
+    for (int i = threadIdx.x + HELD * blockDim.x; i < n; i += blockDim.x) {
         const int ch = part * n + i;
         out[ch] = from_f32<T>(value(ch) * inv * (a.norm_w ? a.norm_w[ch] : 1.f));
     }
