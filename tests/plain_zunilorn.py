@@ -97,7 +97,7 @@ def attention(m: dict, w: dict, p: str, h: torch.Tensor) -> torch.Tensor:
 
 
 def causal_conv(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
-    """x [T, C], weight [C, taps] whose last column meets the current token; zeros before the start."""
+    """x [T, C], weight [C, taps]: column taps - 1 - d weighs the input d positions back; nothing lies before position 0."""
     T, taps = x.shape[0], weight.shape[1]
     padded = torch.cat([torch.zeros(taps - 1, x.shape[1], dtype=x.dtype), x], 0)
     out = bias.expand(T, -1).clone()

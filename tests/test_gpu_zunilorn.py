@@ -461,7 +461,7 @@ def test_the_sink_takes_its_share_and_the_cap_bends_the_scores(dtype, tmp_path):
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_the_first_tokens_of_a_sequence(dtype):
-    """Positions 0, 1, 2: one key and the sink; a convolution that reaches before the start."""
+    """Positions 0, 1, 2: one key and the sink; a convolution that reaches back beyond position 0."""
     from kipp_b200.engine import StepEntry
     for name in ("A", "D"):
         toks = random_tokens(CONFIGS[name]["vocab"], 3, seed=70)

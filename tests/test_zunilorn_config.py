@@ -156,7 +156,7 @@ def test_plain_state_space_of_one_head_by_hand():
     assert torch.allclose(got[:, 0], torch.tensor(want, dtype=torch.float64), atol=1e-12)
 
 
-def test_plain_sink_counts_once_and_has_no_value():
+def test_plain_sink_joins_the_denominator_alone():
     m = {"heads": 1, "kv_heads": 1, "dim": 2, "vdim": 1, "scale": 1.0}
     w = {"q": torch.zeros(2, 2, dtype=torch.float64), "k": torch.zeros(2, 2, dtype=torch.float64),
          "v": torch.tensor([[1.0, 0.0]], dtype=torch.float64), "g": torch.zeros(1, 2, dtype=torch.float64),
