@@ -55,6 +55,7 @@ class ModelSpec:
     embedding_prefix: str = ""       # prefix of a single embedding stage
     max_positions: Optional[int] = None
     plan: Optional[dict] = None      # a plan made by the library's own builder stands for the parts
+    streams: int = 1                 # copies of the residual stream (blocks joined by hyper-connections)
 
     def embedding_stages(self) -> list:
         if isinstance(self.embedding, (list, tuple)):
@@ -69,7 +70,7 @@ class ModelSpec:
         cfg = self.config.to_dict() if hasattr(self.config, "to_dict") else None
         plan = {
             "hidden_size": self.hidden_size, "vocab_size": self.vocab_size,
-            "max_positions": self.max_positions, "config": cfg,
+            "max_positions": self.max_positions, "streams": self.streams, "config": cfg,
             "embedding": [{"prefix": p, "part": part.describe(p, ctx)} for p, part in self.embedding_stages()],
             "layers": [{"prefix": p, "part": block.describe(p, ctx)} for p, block in self.layers],
             "order": [{"layer": r.layer, "cache": r.cache, "writes_cache": r.writes_cache} for r in self.order],
@@ -95,4 +96,4 @@ class ModelSpec:
                    embedding=None, layers=[], order=[LayerRun(o["layer"], o["cache"], o["writes_cache"])
                                                      for o in plan["order"]],
                    final_norm=(plan["final_norm"]["prefix"], None), head=(plan["head"]["prefix"], None),
-                   max_positions=plan.get("max_positions"), plan=plan)
+                   max_positions=plan.get("max_positions"), plan=plan, streams=plan.get("streams", 1))

@@ -32,7 +32,8 @@ class AttentionMixer(Mixer):
                  window: Optional[int] = None, scale: Optional[float] = None, *,
                  value_dim: Optional[int] = None, keep_first: int = 0, head_mix: bool = False,
                  output_scale: float = 1.0, bias: bool = False, score_maps: int = 1, combine_maps: bool = False,
-                 lambda_init: float = 0.0, combine_eps: float = 1e-5, names: Optional[dict] = None):
+                 lambda_init: float = 0.0, combine_eps: float = 1e-5, names: Optional[dict] = None,
+                 sink: str = "none", head_gate: bool = False, softcap: float = 0.0, **more):
         if num_heads % num_kv_heads:
             raise ValueError("num_heads must be a multiple of num_kv_heads")
         self.hidden_size = hidden_size
@@ -49,6 +50,10 @@ class AttentionMixer(Mixer):
         self.output_scale, self.names = output_scale, dict(names or {})
         self.bias, self.score_maps, self.combine_maps = bias, score_maps, combine_maps
         self.lambda_init, self.combine_eps = lambda_init, combine_eps
+        # sink: none, learned (a number per head in the softmax's denominator) or unit; head_gate: a sigmoid gate
+        # per head from the mixer's input; softcap c > 0: scores c tanh(s / c); `more`: further options of the
+        # part by their plan names (norm_whole, interleaved, chunk, values_are_keys, shared_kv)
+        self.sink, self.head_gate, self.softcap, self.more = sink, bool(head_gate), float(softcap), dict(more)
 
     def cache_spec(self) -> PagedKVSpec:
         # (the maps of a key head lie side by side in one row of the key pages)
@@ -63,4 +68,5 @@ class AttentionMixer(Mixer):
                 "value_dim": int(self.value_dim or 0), "keep_first": int(self.keep_first),
                 "head_mix": bool(self.head_mix), "output_scale": float(self.output_scale), "bias": bool(self.bias),
                 "score_maps": int(self.score_maps), "combine_maps": bool(self.combine_maps),
-                "lambda_init": float(self.lambda_init), "combine_eps": float(self.combine_eps), "names": self.names}
+                "lambda_init": float(self.lambda_init), "combine_eps": float(self.combine_eps), "names": self.names,
+                "sink": self.sink, "head_gate": self.head_gate, "softcap": self.softcap, **self.more}

@@ -27,12 +27,15 @@ class OutputHead(Part):
     in when the checkpoint has no head of its own."""
     kind = "output_head"
 
-    def __init__(self, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None, weight_name: str = "weight"):
+    def __init__(self, vocab_size: int, hidden_size: int, tied_to: Optional[str] = None, weight_name: str = "weight",
+                 logit_scale: float = 1.0, logit_softcap: float = 0.0):
         self.vocab_size = vocab_size
         self.hidden_size = hidden_size
         self.tied_to = tied_to
         self.weight_name = weight_name
+        # logits * logit_scale, then (logit_softcap c > 0) c tanh(logits / c)
+        self.logit_scale, self.logit_softcap = float(logit_scale), float(logit_softcap)
 
     def params(self, prefix, ctx) -> dict:
         return {"vocab_size": self.vocab_size, "hidden_size": self.hidden_size, "tied_to": self.tied_to,
-                "weight_name": self.weight_name}
+                "weight_name": self.weight_name, "logit_scale": self.logit_scale, "logit_softcap": self.logit_softcap}

@@ -93,3 +93,22 @@ class GatedMemoryMixer(Mixer):
         if self.query_scale is not None:
             out["query_scale"] = float(self.query_scale)
         return out
+
+
+class StateSpaceMixer(Mixer):
+    """The selective state space layer in its matrix-state form: one projection
+    [z | x | B | C | dt], a causal convolution of ``conv`` taps over x, B and C,
+    S_t = exp(-exp(A) dt) S_(t-1) + dt B_t x_t^T per head (the heads of a group share
+    B and C), y = S^T C + D x, the gate silu(z), a root-mean-square division in
+    ``norm_groups`` parts.  Per request: S and the convolution's last inputs."""
+    kind = "state_space"
+
+    def __init__(self, hidden_size: int, num_heads: int, value_dim: int, state_dim: int, conv: int, eps: float, *,
+                 groups: int = 1, norm_groups: int = 1, names: Optional[dict] = None):
+        self.hidden_size, self.num_heads, self.value_dim, self.state_dim = hidden_size, num_heads, value_dim, state_dim
+        self.conv, self.eps, self.groups, self.norm_groups, self.names = conv, eps, groups, norm_groups, dict(names or {})
+
+    def params(self, prefix, ctx) -> dict:
+        return {"hidden_size": self.hidden_size, "num_heads": self.num_heads, "value_dim": self.value_dim,
+                "state_dim": self.state_dim, "conv": self.conv, "eps": self.eps, "groups": self.groups,
+                "norm_groups": self.norm_groups, "names": self.names}

@@ -77,3 +77,40 @@ class StretchedRotaryEncoding(RotaryEncoding):
     def describe(self, prefix, ctx) -> dict:
         return {"kind": "stretched_rotary", "head_dim": self.head_dim, "theta": self.theta, "rotary_dim": self.rotary_dim,
                 "factor": self.factor, "low": self.low, "high": self.high, "original": self.original}
+
+
+class YarnRotaryEncoding(RotaryEncoding):
+    """Rotary frequencies scaled by a ramp over the pair index: with
+    pair(t) = dims ln(original / (2 pi t)) / (2 ln theta), lo = max(floor(pair(fast)), 0),
+    hi = min(ceil(pair(slow)), dims - 1) and ramp_i = clamp((i - lo) / max(hi - lo, 0.001), 0, 1)
+    the frequency of pair i is f_i / factor * ramp_i + f_i (1 - ramp_i); cos and sin
+    are both multiplied by 0.1 ln(factor) + 1."""
+    kind = "yarn_rotary"
+
+    def __init__(self, head_dim: int, theta: float, factor: float, original: float, fast: float, slow: float,
+                 rotary_dim: Optional[int] = None):
+        super().__init__(head_dim, theta, rotary_dim)
+        self.factor, self.original, self.fast, self.slow = float(factor), float(original), float(fast), float(slow)
+
+    def magnitude(self) -> float:
+        import math
+        return 0.1 * math.log(self.factor) + 1.0
+
+    def frequencies(self) -> torch.Tensor:
+        import math
+        dims = self.rotary_dim
+        pair = lambda t: dims * math.log(self.original / (2.0 * math.pi * t)) / (2.0 * math.log(self.theta))   # noqa: E731
+        lo, hi = max(math.floor(pair(self.fast)), 0), min(math.ceil(pair(self.slow)), dims - 1)
+        out = []
+        for i in range(dims // 2):
+            f = self.theta ** (-2.0 * i / dims)
+            ramp = min(max((i - lo) / max(hi - lo, 0.001), 0.0), 1.0)
+            out.append(f / self.factor * ramp + f * (1.0 - ramp))
+        return torch.tensor(out, dtype=torch.float64).float()
+
+    def table_key(self):
+        return ("yarn", self.theta, self.rotary_dim, self.factor, self.original, self.fast, self.slow)
+
+    def describe(self, prefix, ctx) -> dict:
+        return {"kind": "yarn_rotary", "head_dim": self.head_dim, "theta": self.theta, "rotary_dim": self.rotary_dim,
+                "factor": self.factor, "original": self.original, "fast": self.fast, "slow": self.slow}

@@ -128,6 +128,55 @@ def test_random_weights_cover_every_declared_tensor(tmp_path):
     assert logits.shape == (12, 101) and bool(torch.isfinite(logits).all()) and float(logits.abs().max()) <= 8.0
 
 
+def test_the_parts_can_be_described_from_python_for_another_design():
+    """A model put together in Python from the descriptions of the same parts (the layers without experts) gives
+    the tensors and the parts the library's own builder makes."""
+    from kipp_b200.models.spec import LayerRun, ModelSpec
+    from kipp_b200.parts import (AttentionMixer, GatedFeedForward, HyperConnectionBlock, OutputHead, RMSNorm,
+                                 StateSpaceMixer, TokenEmbedding, YarnRotaryEncoding)
+    cfg = copy.deepcopy(CONFIGS["A"])
+    cfg["layers"] = [cfg["layers"][0], cfg["layers"][3]]
+    cfg.pop("loop")
+    eps, width, S = cfg["norm"]["eps"], cfg["width"], cfg["streams"]
+    layers = []
+    for i, layer in enumerate(cfg["layers"]):
+        m = layer["mixer"]
+        if layer["type"] == "mamba2":
+            mixer = StateSpaceMixer(width, m["heads"], m["vdim"], m["state"], m["conv"], eps, groups=m["groups"],
+                                    norm_groups=m["norm_groups"])
+        else:
+            sc = m["rot"]["scaling"]
+            pos = YarnRotaryEncoding(m["dim"], m["rot"]["base"], sc["factor"], sc["original"], sc["fast"], sc["slow"], m["rot"]["dims"])
+            mixer = AttentionMixer(width, m["heads"], m["kv_heads"], m["dim"], pos, None, 0, m["scale"], value_dim=m["vdim"],
+                                   sink="learned", head_gate=True, softcap=m["softcap"],
+                                   names={"q": "q", "k": "k", "v": "v", "o": "o", "sink": "sink", "gate": "g"})
+        f = layer["mlp"]
+        ffn = GatedFeedForward(width, f["ff"], limit=f["limit"], alpha=1.702, bias=True) if f else None
+        layers.append((f"l{i}.", HyperConnectionBlock(RMSNorm(width, eps, "norm1"), mixer, RMSNorm(width, eps, "norm2") if f else None,
+                                                      ffn, streams=S, residual_mult=cfg["residual_mult"])))
+    spec = ModelSpec(config=None, hidden_size=width, vocab_size=cfg["vocab"], streams=S,
+                     embedding=TokenEmbedding(cfg["vocab"], width, weight_name="embed"), layers=layers,
+                     order=[LayerRun(i, i) for i in range(len(layers))], final_norm=("", RMSNorm(width, eps, "final.norm")),
+                     head=("", OutputHead(cfg["vocab"], width, tied_to="embed", weight_name="head",
+                                          logit_softcap=cfg["logit_softcap"])))
+    mine = {s.name: tuple(s.shape) for s in spec.tensor_specs()}
+    theirs_spec = spec_of(cfg)
+    assert mine == {s.name: tuple(s.shape) for s in theirs_spec.tensor_specs()}
+    plan, _ = spec.to_plan()
+    assert plan["streams"] == theirs_spec.plan["streams"] == 3
+    for a, b in zip(plan["layers"], theirs_spec.plan["layers"]):
+        assert a["part"]["mixer"]["kind"] == b["part"]["mixer"]["kind"]
+        for key in ("streams", "connections", "residual_mult"):
+            assert a["part"][key] == b["part"][key]
+    assert plan["layers"][1]["part"]["mixer"]["position"] == theirs_spec.plan["layers"][1]["part"]["mixer"]["position"]
+    assert plan["head"]["part"]["logit_softcap"] == 12.0
+    # a block on another number of copies than the plan's is refused
+    spec.streams = 2
+    with pytest.raises(Exception) as e:
+        spec.tensor_specs()
+    assert "copies of the residual stream" in str(e.value)
+
+
 # ------------------------------------------------------------------ the plain model against hand-made cases
 def test_plain_causal_convolution_and_its_start():
     x = torch.tensor([[1.0], [2.0], [4.0]], dtype=torch.float64)
